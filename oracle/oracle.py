@@ -1,0 +1,158 @@
+"""TEST INFRASTRUCTURE: ctypes binding of ``liboracle.so`` on numpy arrays.
+
+Every wrapper takes and returns numpy arrays (float32/float64, or complex64/complex128 for the
+complex diagonal scans) in the layouts of the reference ops: diagonal ``lam [M,N]``,
+``v [M,L,N]``; selective ``lam, v [B,L,N]``; Mamba ``draw/u/z [B,L,D]``, ``A [D,N]``,
+``Bt/Ct [B,L,N]``; all-pole ``a [lanes,na]``, ``w [lanes,L]``.  The precision of the oracle run
+follows the dtype of the arrays handed in.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import subprocess
+from pathlib import Path
+
+import numpy as np
+
+_HERE = Path(__file__).resolve().parent
+_LIB = None
+
+
+def build(force: bool = False) -> Path:
+    """Compile ``liboracle.so`` with the Makefile beside this file (no-op when up to date)."""
+    if force:
+        subprocess.run(["make", "-C", str(_HERE), "clean"], check=True, capture_output=True)
+    subprocess.run(["make", "-C", str(_HERE)], check=True, capture_output=True)
+    return _HERE / "liboracle.so"
+
+
+def lib() -> ctypes.CDLL:
+    global _LIB
+    if _LIB is None:
+        path = _HERE / "liboracle.so"
+        if not path.exists():
+            build()
+        _LIB = ctypes.CDLL(str(path))
+        _LIB.oracle_num_threads.restype = ctypes.c_int
+    return _LIB
+
+
+def num_threads() -> int:
+    return int(lib().oracle_num_threads())
+
+
+def set_num_threads(n: int) -> None:
+    lib().oracle_set_num_threads(ctypes.c_int(n))
+
+
+def _real_dtype(x: np.ndarray):
+    return {np.dtype("float32"): np.float32, np.dtype("complex64"): np.float32,
+            np.dtype("float64"): np.float64, np.dtype("complex128"): np.float64}[x.dtype]
+
+
+def _sfx(x: np.ndarray) -> str:
+    return "f32" if _real_dtype(x) is np.float32 else "f64"
+
+
+def _c(x):
+    return None if x is None else np.ascontiguousarray(x)
+
+
+def _p(x):
+    return ctypes.c_void_p(None if x is None else x.ctypes.data)
+
+
+def _call(name, sfx, ints, ptrs):
+    fn = getattr(lib(), f"oracle_{name}_{sfx}")
+    fn.restype = None
+    fn(*[ctypes.c_int64(i) for i in ints[0]], *[ctypes.c_int(i) for i in ints[1]], *[_p(p) for p in ptrs])
+
+
+# ------------------------------------------------------------------ S1 / S2
+def _diag_like(name, lam, v, x0):
+    lam, v, x0 = _c(lam), _c(v), _c(x0)
+    M, L, N = v.shape
+    out = np.empty_like(v)
+    _call(name, _sfx(v), ((M, L, N), (int(np.iscomplexobj(v)),)), (lam, v, x0, out))
+    return out
+
+
+def _diag_like_bwd(name, g, lam, out, x0):
+    g, lam, out, x0 = _c(g), _c(lam), _c(out), _c(x0)
+    M, L, N = out.shape
+    glam = np.empty_like(lam)
+    gv = np.empty_like(out)
+    gx0 = np.empty_like(x0) if x0 is not None else None
+    _call(name, _sfx(out), ((M, L, N), (int(np.iscomplexobj(out)),)), (g, lam, out, x0, glam, gv, gx0))
+    return glam, gv, gx0
+
+
+def diag_fwd(lam, v, x0=None):
+    """S1 forward: ``lam [M,N]`` constant over time."""
+    return _diag_like("diag_fwd", lam, v, x0)
+
+
+def diag_bwd(g, lam, out, x0=None):
+    """S1 adjoint → ``(glam [M,N], gv [M,L,N], gx0 [M,N] | None)``."""
+    return _diag_like_bwd("diag_bwd", g, lam, out, x0)
+
+
+def sel_fwd(lam, v, x0=None):
+    """S2 forward: ``lam [B,L,N]`` time-varying."""
+    return _diag_like("sel_fwd", lam, v, x0)
+
+
+def sel_bwd(g, lam, out, x0=None):
+    """S2 adjoint → ``(glam [B,L,N], gv [B,L,N], gx0 [B,N] | None)``."""
+    return _diag_like_bwd("sel_bwd", g, lam, out, x0)
+
+
+# ------------------------------------------------------------------ S3
+def mamba_fwd(draw, A, Bt, Ct, u, z, Dp, h0=None):
+    draw, A, Bt, Ct, u, z, Dp, h0 = map(_c, (draw, A, Bt, Ct, u, z, Dp, h0))
+    B, L, D = draw.shape
+    N = A.shape[-1]
+    assert N <= 256
+    out = np.empty_like(draw)
+    hlast = np.empty((B, D, N), dtype=draw.dtype)
+    _call("mamba_fwd", _sfx(draw), ((B, L, D, N), ()), (draw, A, Bt, Ct, u, z, Dp, h0, out, hlast))
+    return out, hlast
+
+
+def mamba_bwd(draw, A, Bt, Ct, u, z, Dp, h0, gout, ghlast=None):
+    """S3 adjoint → dict with gdraw, gA, gBt, gCt, gu, gz, gDp, gh0 (None without h0)."""
+    draw, A, Bt, Ct, u, z, Dp, h0, gout, ghlast = map(_c, (draw, A, Bt, Ct, u, z, Dp, h0, gout, ghlast))
+    B, L, D = draw.shape
+    N = A.shape[-1]
+    dt = draw.dtype
+    r = dict(gdraw=np.empty_like(draw), gA=np.empty((D, N), dt), gBt=np.empty((B, L, N), dt),
+             gCt=np.empty((B, L, N), dt), gu=np.empty_like(draw), gz=np.empty_like(draw),
+             gDp=np.empty((D,), dt), gh0=(np.empty((B, D, N), dt) if h0 is not None else None))
+    _call("mamba_bwd", _sfx(draw), ((B, L, D, N), ()),
+          (draw, A, Bt, Ct, u, z, Dp, h0, gout, ghlast, r["gdraw"], r["gA"], r["gBt"], r["gCt"],
+           r["gu"], r["gz"], r["gDp"], r["gh0"]))
+    return r
+
+
+# ------------------------------------------------------------------ S4
+def allpole_fwd(a, w, y0=None):
+    a, w, y0 = _c(a), _c(w), _c(y0)
+    lanes, L = w.shape
+    na = a.shape[-1]
+    assert 1 <= na <= 16
+    y = np.empty_like(w)
+    _call("allpole_fwd", _sfx(w), ((lanes, L, na), ()), (a, w, y0, y))
+    return y
+
+
+def allpole_bwd(g, a, y, y0=None):
+    """S4 adjoint → ``(grad_a [lanes,na], gw [lanes,L], grad_y0 [lanes,na] | None)``."""
+    g, a, y, y0 = _c(g), _c(a), _c(y), _c(y0)
+    lanes, L = y.shape
+    na = a.shape[-1]
+    ga = np.empty_like(a)
+    gw = np.empty_like(y)
+    gy0 = np.empty_like(y0) if y0 is not None else None
+    _call("allpole_bwd", _sfx(y), ((lanes, L, na), ()), (g, a, y, y0, ga, gw, gy0))
+    return ga, gw, gy0
