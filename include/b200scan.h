@@ -1,0 +1,73 @@
+/* C ABI of libb200scan: recurrent-scan kernels for NVIDIA B200 (sm_100a).
+ *
+ * Plain pointers and sizes only.  Every tensor argument is a DEVICE pointer to a dense,
+ * contiguous buffer in the layout stated per function; complex64 is interleaved (re, im)
+ * float pairs.  `stream` is a cudaStream_t passed as void*.  All work is enqueued on that
+ * stream; no entry point synchronises, allocates or frees device memory (so calls are legal
+ * during CUDA-graph capture), and none keeps mutable global state, so concurrent calls from
+ * several host threads are fine as long as each uses its own workspace.
+ *
+ * Return value: B200_OK, or a B200_ERR_* code for an argument the host side can reject.  A
+ * kernel that gives up on a bounded wait records B200_ERR_TIMEOUT in its workspace header;
+ * b200_workspace_status() reads that word back (it synchronises the stream).
+ *
+ * Paths in the "replaces" notes are relative to the tsfast project root (v0.5.0).
+ */
+#ifndef B200SCAN_H_
+#define B200SCAN_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200_OK 0
+#define B200_ERR_ARG 1         /* null pointer, non-positive size, unknown dtype */
+#define B200_ERR_WORKSPACE 2   /* workspace missing, misaligned or too small */
+#define B200_ERR_LAUNCH 3      /* the CUDA runtime refused a memset or a launch */
+#define B200_ERR_UNSUPPORTED 4 /* size outside what the kernel handles */
+#define B200_ERR_TIMEOUT 5     /* device side: a look-back wait ran out of polls */
+
+#define B200_F32 0 /* float32 */
+#define B200_C64 1 /* complex64, interleaved */
+
+/* Library version (major*100 + minor). */
+int b200_version(void);
+
+/* Read the error word of a workspace after the work enqueued on `stream` has finished.
+ * Synchronises `stream`.  Returns B200_OK or the B200_ERR_* code a kernel recorded. */
+int b200_workspace_status(const void* workspace, void* stream);
+
+/* ---- S1: diagonal scan with time-invariant coefficients -------------------------------
+ * x_t = lam * x_{t-1} + v_t.   lam [M,N], v/out [M,L,N], x0 [M,N] or NULL (zero start).
+ * Replaces diag_fwd / diag_bwd of tsfast/models/_core/scan_backends/diagonal_c.py:413-442
+ * (CPU) and _diag_fwd_kernel / _diag_bwd_kernel of scan_backends/diagonal_triton.py:82-228,
+ * i.e. the bodies of the ops tsfast::scan_diagonal(_bwd) in tsfast/models/_core/scan.py:100-134.
+ * Backward: g [M,L,N] upstream gradient, out = forward result; writes glam [M,N] (per lane,
+ * summed over time), gv [M,L,N] and, when x0 != NULL, gx0 [M,N] (gx0 may be NULL otherwise). */
+size_t b200_diag_workspace_bytes(int dtype, int backward, int64_t M, int64_t L, int64_t N);
+int b200_diag_fwd(int dtype, int64_t M, int64_t L, int64_t N, const void* lam, const void* v,
+                  const void* x0, void* out, void* workspace, size_t workspace_bytes, void* stream);
+int b200_diag_bwd(int dtype, int64_t M, int64_t L, int64_t N, const void* g, const void* lam,
+                  const void* out, const void* x0, void* glam, void* gv, void* gx0,
+                  void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- S2: diagonal scan with time-varying coefficients ---------------------------------
+ * x_t = lam_t * x_{t-1} + v_t.   lam, v, out [B,L,N]; x0 [B,N] or NULL.
+ * Replaces sel_fwd / sel_bwd of tsfast/models/_core/scan_backends/selective_c.py:52-120 (CPU)
+ * and _sel_fwd / _sel_bwd of scan_backends/selective_triton.py:48-109, i.e. the bodies of
+ * tsfast::scan_selective(_bwd) in tsfast/models/_core/scan.py:157-195; complex64 follows the
+ * doubling-scan semantics there.  Backward writes glam [B,L,N], gv [B,L,N], gx0 [B,N]. */
+size_t b200_sel_workspace_bytes(int dtype, int backward, int64_t B, int64_t L, int64_t N);
+int b200_sel_fwd(int dtype, int64_t B, int64_t L, int64_t N, const void* lam, const void* v,
+                 const void* x0, void* out, void* workspace, size_t workspace_bytes, void* stream);
+int b200_sel_bwd(int dtype, int64_t B, int64_t L, int64_t N, const void* g, const void* lam,
+                 const void* out, const void* x0, void* glam, void* gv, void* gx0,
+                 void* workspace, size_t workspace_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200SCAN_H_ */

@@ -100,27 +100,40 @@ void ORA(diag_bwd)(int64_t M, int64_t L, int64_t N, int is_complex, const REAL* 
  * the complex case follows the doubling-scan semantics of scan.py:157-170. */
 void ORA(sel_fwd)(int64_t B, int64_t L, int64_t N, int is_complex, const REAL* lam,
                   const REAL* v, const REAL* x0, REAL* out) {
-#pragma omp parallel for collapse(2) schedule(static)
-    for (int64_t b = 0; b < B; ++b) {
-        for (int64_t n = 0; n < N; ++n) {
-            const int64_t ln = b * N + n;
-            if (is_complex) {
-                REAL xr = x0 ? x0[2 * ln] : (REAL)0, xi = x0 ? x0[2 * ln + 1] : (REAL)0;
-                for (int64_t t = 0; t < L; ++t) {
-                    const int64_t p = 2 * ((b * L + t) * N + n);
-                    const REAL ar = lam[p], ai = lam[p + 1];
-                    const REAL nr = ar * xr - ai * xi + v[p];
-                    xi = ar * xi + ai * xr + v[p + 1];
-                    xr = nr;
-                    out[p] = xr;
-                    out[p + 1] = xi;
+    /* one task per (row, 64-lane tile), time outermost inside the task so that every step
+     * touches one contiguous run, as selective_c.py:44-76 does (TILE = 64) */
+    const int64_t TILE = 64, nt = (N + TILE - 1) / TILE;
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < B * nt; ++i) {
+        const int64_t b = i / nt, n0 = (i % nt) * TILE;
+        const int nw = (int)((N - n0) < TILE ? (N - n0) : TILE);
+        REAL xr[64], xi[64];
+        if (is_complex) {
+            for (int j = 0; j < nw; ++j) {
+                xr[j] = x0 ? x0[2 * (b * N + n0 + j)] : (REAL)0;
+                xi[j] = x0 ? x0[2 * (b * N + n0 + j) + 1] : (REAL)0;
+            }
+            for (int64_t t = 0; t < L; ++t) {
+                const int64_t p = 2 * ((b * L + t) * N + n0);
+                for (int j = 0; j < nw; ++j) {
+                    const REAL ar = lam[p + 2 * j], ai = lam[p + 2 * j + 1];
+                    const REAL nr = ar * xr[j] - ai * xi[j] + v[p + 2 * j];
+                    xi[j] = ar * xi[j] + ai * xr[j] + v[p + 2 * j + 1];
+                    xr[j] = nr;
+                    out[p + 2 * j] = xr[j];
+                    out[p + 2 * j + 1] = xi[j];
                 }
-            } else {
-                REAL x = x0 ? x0[ln] : (REAL)0;
-                for (int64_t t = 0; t < L; ++t) {
-                    const int64_t p = (b * L + t) * N + n;
-                    x = lam[p] * x + v[p];
-                    out[p] = x;
+            }
+        } else {
+            for (int j = 0; j < nw; ++j) xr[j] = x0 ? x0[b * N + n0 + j] : (REAL)0;
+            for (int64_t t = 0; t < L; ++t) {
+                const int64_t p = (b * L + t) * N + n0;
+                const REAL* lr = lam + p;
+                const REAL* vr = v + p;
+                REAL* orr = out + p;
+                for (int j = 0; j < nw; ++j) {
+                    xr[j] = lr[j] * xr[j] + vr[j];
+                    orr[j] = xr[j];
                 }
             }
         }
@@ -133,49 +146,66 @@ void ORA(sel_fwd)(int64_t B, int64_t L, int64_t N, int is_complex, const REAL* l
 void ORA(sel_bwd)(int64_t B, int64_t L, int64_t N, int is_complex, const REAL* g,
                   const REAL* lam, const REAL* out, const REAL* x0, REAL* glam, REAL* gv,
                   REAL* gx0) {
-#pragma omp parallel for collapse(2) schedule(static)
-    for (int64_t b = 0; b < B; ++b) {
-        for (int64_t n = 0; n < N; ++n) {
-            const int64_t ln = b * N + n;
-            if (is_complex) {
-                REAL Gr = 0, Gi = 0;
-                for (int64_t t = L - 1; t >= 0; --t) {
-                    const int64_t p = 2 * ((b * L + t) * N + n);
+    const int64_t TILE = 64, nt = (N + TILE - 1) / TILE;
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < B * nt; ++i) {
+        const int64_t b = i / nt, n0 = (i % nt) * TILE;
+        const int nw = (int)((N - n0) < TILE ? (N - n0) : TILE);
+        REAL Gr[64], Gi[64];
+        for (int j = 0; j < nw; ++j) Gr[j] = Gi[j] = 0;
+        if (is_complex) {
+            for (int64_t t = L - 1; t >= 0; --t) {
+                const int64_t p = 2 * ((b * L + t) * N + n0);
+                for (int j = 0; j < nw; ++j) {
+                    const int64_t q = p + 2 * j, ln = b * N + n0 + j;
                     if (t + 1 < L) {
-                        const REAL ar = lam[p + 2 * N], ai = -lam[p + 2 * N + 1];
-                        const REAL nr = g[p] + ar * Gr - ai * Gi;
-                        Gi = g[p + 1] + ar * Gi + ai * Gr;
-                        Gr = nr;
+                        const REAL ar = lam[q + 2 * N], ai = -lam[q + 2 * N + 1];
+                        const REAL nr = g[q] + ar * Gr[j] - ai * Gi[j];
+                        Gi[j] = g[q + 1] + ar * Gi[j] + ai * Gr[j];
+                        Gr[j] = nr;
                     } else {
-                        Gr = g[p];
-                        Gi = g[p + 1];
+                        Gr[j] = g[q];
+                        Gi[j] = g[q + 1];
                     }
-                    gv[p] = Gr;
-                    gv[p + 1] = Gi;
+                    gv[q] = Gr[j];
+                    gv[q + 1] = Gi[j];
                     REAL xr, xi;
                     if (t > 0) {
-                        xr = out[p - 2 * N];
-                        xi = out[p - 2 * N + 1];
+                        xr = out[q - 2 * N];
+                        xi = out[q - 2 * N + 1];
                     } else {
                         xr = x0 ? x0[2 * ln] : (REAL)0;
                         xi = x0 ? x0[2 * ln + 1] : (REAL)0;
                     }
-                    glam[p] = Gr * xr + Gi * xi;
-                    glam[p + 1] = Gi * xr - Gr * xi;
+                    glam[q] = Gr[j] * xr + Gi[j] * xi;
+                    glam[q + 1] = Gi[j] * xr - Gr[j] * xi;
                     if (t == 0 && x0) {
-                        const REAL ar = lam[p], ai = -lam[p + 1];
-                        gx0[2 * ln] = ar * Gr - ai * Gi;
-                        gx0[2 * ln + 1] = ar * Gi + ai * Gr;
+                        const REAL ar = lam[q], ai = -lam[q + 1];
+                        gx0[2 * ln] = ar * Gr[j] - ai * Gi[j];
+                        gx0[2 * ln + 1] = ar * Gi[j] + ai * Gr[j];
                     }
                 }
-            } else {
-                REAL G = 0;
-                for (int64_t t = L - 1; t >= 0; --t) {
-                    const int64_t p = (b * L + t) * N + n;
-                    G = (t + 1 < L) ? g[p] + lam[p + N] * G : g[p];
-                    gv[p] = G;
-                    glam[p] = G * (t > 0 ? out[p - N] : (x0 ? x0[ln] : (REAL)0));
-                    if (t == 0 && x0) gx0[ln] = lam[p] * G;
+            }
+        } else {
+            for (int64_t t = L - 1; t >= 0; --t) {
+                const int64_t p = (b * L + t) * N + n0;
+                const REAL* gr = g + p;
+                REAL* gvr = gv + p;
+                REAL* glr = glam + p;
+                if (t + 1 < L) {
+                    const REAL* ln_ = lam + p + N;
+                    for (int j = 0; j < nw; ++j) Gr[j] = gr[j] + ln_[j] * Gr[j];
+                } else {
+                    for (int j = 0; j < nw; ++j) Gr[j] = gr[j];
+                }
+                for (int j = 0; j < nw; ++j) gvr[j] = Gr[j];
+                if (t > 0) {
+                    const REAL* op = out + p - N;
+                    for (int j = 0; j < nw; ++j) glr[j] = Gr[j] * op[j];
+                } else {
+                    for (int j = 0; j < nw; ++j) glr[j] = Gr[j] * (x0 ? x0[b * N + n0 + j] : (REAL)0);
+                    if (x0)
+                        for (int j = 0; j < nw; ++j) gx0[b * N + n0 + j] = lam[p + j] * Gr[j];
                 }
             }
         }

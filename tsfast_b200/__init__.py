@@ -1,0 +1,20 @@
+"""tsfast_b200: B200-native (sm_100a) recurrent-scan kernels behind tsfast's scan interfaces.
+
+Public surface:
+
+* ``diagonal_recurrence`` / ``selective_recurrence`` – the scan functions, same signatures as
+  ``tsfast.models._core.scan``;
+* ``scan_backends.diagonal_b200`` / ``selective_b200`` – backend modules speaking tsfast's
+  ``supports/forward/backward`` protocol;
+* ``install()`` / ``uninstall()`` – plug those modules into an importable tsfast so that its LRU,
+  S5, Mamba and dynoNet modules dispatch to these kernels.
+
+Everything runs through ``libb200scan.so`` (``python -m tsfast_b200.build``); nothing here falls
+back to PyTorch or the CPU.
+"""
+
+from .scan import diagonal_recurrence, selective_recurrence
+from .install import install, uninstall
+
+__all__ = ["diagonal_recurrence", "selective_recurrence", "install", "uninstall"]
+__version__ = "0.1.0"

@@ -1,0 +1,49 @@
+"""Plug the B200 backend modules into tsfast's dispatch registries.
+
+tsfast resolves a fused kernel per call through ``dispatch.resolve(op, registry, auto_order,
+args)`` (``tsfast/models/_core/dispatch.py:80-135``); a registry maps a backend family name to a
+module object.  ``"triton"`` is the family tsfast tries first on CUDA under ``"auto"``
+(``_core/scan.py:42``), so ``install()`` swaps these modules in under that key and
+``uninstall()`` restores what was there.  tsfast itself is not modified and need not be present
+for the rest of this package to work.
+"""
+
+from __future__ import annotations
+
+import importlib
+
+_saved: dict[tuple[str, str], object] = {}
+_KEY = "triton"
+
+
+def _targets():
+    """(registry dict, slot name, replacement module) for every registry tsfast exposes."""
+    from .scan_backends import diagonal_b200, selective_b200
+
+    scan = importlib.import_module("tsfast.models._core.scan")
+    out = [(scan._BACKENDS["diagonal"], "scan.diagonal", diagonal_b200),
+           (scan._BACKENDS["selective"], "scan.selective", selective_b200)]
+    return out
+
+
+def install() -> list[str]:
+    """Route tsfast's CUDA scan dispatch to the B200 kernels; returns the slots replaced."""
+    done = []
+    for registry, slot, mod in _targets():
+        if (slot, _KEY) not in _saved:
+            _saved[(slot, _KEY)] = registry.get(_KEY)
+        registry[_KEY] = mod
+        done.append(slot)
+    return done
+
+
+def uninstall() -> None:
+    """Restore tsfast's own backends."""
+    if not _saved:
+        return
+    for registry, slot, _ in _targets():
+        old = _saved.pop((slot, _KEY), None)
+        if old is None:
+            registry.pop(_KEY, None)
+        else:
+            registry[_KEY] = old
