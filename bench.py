@@ -198,21 +198,36 @@ def run_gpu(args):
     ms = e0.elapsed_time(e1) / args.steps
     clock_rec = clocks.stop() if rank == 0 else None
 
-    # ---- per-kernel durations (forward, adjoint) with events around each launch
-    kf, kb = [], []
-    for _ in range(max(3, min(args.steps, 10))):
-        s0, s1, s2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
-        s0.record()
-        h = sel.forward(a, b, None)
-        s1.record()
+    # ---- per-kernel durations: n back-to-back launches of one kernel between two events
+    n = max(3, min(args.steps, 10))
+    h = sel.forward(a, b, None)
+    s0, s1, s2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+    torch.cuda.synchronize()
+    s0.record()
+    for _ in range(n):
+        sel.forward(a, b, None)
+    s1.record()
+    for _ in range(n):
         sel.backward(g, a, h, None)
-        s2.record()
-        torch.cuda.synchronize()
-        kf.append(s0.elapsed_time(s1))
-        kb.append(s1.elapsed_time(s2))
-    fwd_ms, bwd_ms = statistics.mean(kf), statistics.mean(kb)
+    s2.record()
+    torch.cuda.synchronize()
+    fwd_ms, bwd_ms = s0.elapsed_time(s1) / n, s1.elapsed_time(s2) / n
 
-    # ---- end to end through the public API from pinned host buffers
+    e2e_ms = float("nan")
+    if not args.kernel_only:
+        e2e_ms = _e2e(args, torch, tsfast_b200, dev, a, b, g, barrier)
+
+    times = torch.tensor([ms, e2e_ms], device=dev)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms, e2e_ms = (float(x) for x in times.tolist())
+    _report(args, world, rank, ms, e2e_ms, fwd_ms, bwd_ms, clock_rec)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def _e2e(args, torch, tsfast_b200, dev, a, b, g, barrier):
+    """Same step through the public API from pinned host buffers, copies inside the timed region."""
     ha, hb, hg = (torch.empty(B, T, D, pin_memory=True).copy_(t) for t in (a, b, g))
     ho, hga, hgb = (torch.empty(B, T, D, pin_memory=True) for _ in range(3))
 
@@ -235,20 +250,17 @@ def run_gpu(args):
         e2e_step()
     t1.record()
     barrier()
-    e2e_ms = t0.elapsed_time(t1) / e2e_steps
+    return t0.elapsed_time(t1) / e2e_steps
 
-    times = torch.tensor([ms, e2e_ms], device=dev)
-    if world > 1:
-        dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    ms, e2e_ms = (float(x) for x in times.tolist())
 
+def _report(args, world, rank, ms, e2e_ms, fwd_ms, bwd_ms, clock_rec):
     if rank == 0:
         peak, peak_src = _peaks()
         value = STEP_BYTES * world / (ms * 1e-3) / 1e9
         bwd_gbs = BWD_BYTES / (bwd_ms * 1e-3) / 1e9
         fwd_gbs = FWD_BYTES / (fwd_ms * 1e-3) / 1e9
         base = None
-        if world == 1 and not args.no_cpu:
+        if world == 1 and not args.no_cpu and not args.kernel_only:
             base = cpu_sample()[0]
         line = {
             "metric": METRIC, "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": args.steps,
@@ -258,7 +270,7 @@ def run_gpu(args):
                        "state_elements_per_s": round(2 * B * T * D * world / (ms * 1e-3)),
                        "l2": "each of the 8 streamed tensors is 268 MB, larger than the 126 MB L2; no flush needed",
                        "sharding": "independent sequences per rank, no collective"},
-            "roofline": {"bound": "hbm", "kernel": "diag_scan_kernel<float, varying, adjoint>",
+            "roofline": {"bound": "hbm", "kernel": "diag_stream_kernel<float, varying, adjoint> (b200_sel_bwd)",
                          "achieved": round(bwd_gbs, 1), "peak": peak, "unit": "GB/s",
                          "frac": round(bwd_gbs / peak, 4), "traffic": None, "peak_source": peak_src,
                          "algorithmic_bytes_per_launch": BWD_BYTES, "ms_per_launch": round(bwd_ms, 4),
@@ -266,9 +278,10 @@ def run_gpu(args):
                                             "algorithmic_bytes_per_launch": FWD_BYTES,
                                             "ms_per_launch": round(fwd_ms, 4)}},
             "cpu_baseline": base,
-            "e2e": {"value": round(STEP_BYTES * world / (e2e_ms * 1e-3) / 1e9, 2), "unit": "GB/s",
-                    "h2d_bytes_per_step": 3 * TENSOR_BYTES, "d2h_bytes_per_step": 3 * TENSOR_BYTES,
-                    "ms_per_step": round(e2e_ms, 3)},
+            "e2e": None if args.kernel_only else {
+                "value": round(STEP_BYTES * world / (e2e_ms * 1e-3) / 1e9, 2), "unit": "GB/s",
+                "h2d_bytes_per_step": 3 * TENSOR_BYTES, "d2h_bytes_per_step": 3 * TENSOR_BYTES,
+                "ms_per_step": round(e2e_ms, 3)},
             "gpu_launches": 2 * args.steps,
             "clocks": clock_rec,
         }
@@ -276,8 +289,6 @@ def run_gpu(args):
         if traffic.exists():  # DRAM bytes per adjoint launch from the committed ncu capture
             line["roofline"]["traffic"] = json.loads(traffic.read_text()).get("sel_bwd_c2_bytes")
         print(json.dumps(line))
-    if world > 1:
-        dist.destroy_process_group()
 
 
 def main():
@@ -287,6 +298,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    ap.add_argument("--kernel-only", action="store_true",
+                    help="device-resident timing only (no end-to-end or CPU leg): the command profiled under ncu")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
