@@ -67,6 +67,19 @@ int b200_sel_bwd(int dtype, int64_t B, int64_t L, int64_t N, const void* g, cons
                  const void* out, const void* x0, void* glam, void* gv, void* gx0,
                  void* workspace, size_t workspace_bytes, void* stream);
 
+/* ---- S4: all-pole IIR scan (dynoNet denominator) -----------------------------------------
+ * y_t = w_t - sum_{i=1..na} a_i y_{t-i}, float32, 1 <= na <= 16.  a, y0 [lanes,na]; w, y
+ * [lanes,L] with time contiguous per lane; y0[j] = y_{-1-j} (newest first) or NULL for a zero
+ * start.  Replaces the generated allpole_fwd / allpole_bwd kernels and the host-side head
+ * corrections of tsfast/models/architectures/dynonet/allpole_triton.py:59-123,174-213, i.e. the
+ * bodies of tsfast::dynonet_allpole(_bwd).  Backward: g upstream gradient, y forward output;
+ * writes grad_a [lanes,na] (finished, with sign and initial-state terms), gw [lanes,L] and, when
+ * y0 != NULL, grad_y0 [lanes,na].  No workspace is needed. */
+int b200_allpole_fwd(int64_t lanes, int64_t L, int64_t na, const void* a, const void* w, const void* y0,
+                     void* y, void* stream);
+int b200_allpole_bwd(int64_t lanes, int64_t L, int64_t na, const void* g, const void* a, const void* y,
+                     const void* y0, void* ga, void* gw, void* gy0, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

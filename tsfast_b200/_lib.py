@@ -36,6 +36,8 @@ SIGNATURES = {
     "b200_sel_workspace_bytes": (_sz, [_int, _int, _i64, _i64, _i64]),
     "b200_sel_fwd": (_int, [_int, _i64, _i64, _i64] + [_vp] * 5 + [_sz, _vp]),
     "b200_sel_bwd": (_int, [_int, _i64, _i64, _i64] + [_vp] * 8 + [_sz, _vp]),
+    "b200_allpole_fwd": (_int, [_i64, _i64, _i64] + [_vp] * 5),
+    "b200_allpole_bwd": (_int, [_i64, _i64, _i64] + [_vp] * 8),
 }
 
 

@@ -1,0 +1,411 @@
+// All-pole IIR scan y_t = w_t - sum_{i=1..na} a_i y_{t-i} per lane (dynoNet G-block denominator),
+// forward and reverse-time adjoint, float32, 1 <= na <= 16.
+//
+// Data layout: w, y, g [lanes, L] with TIME contiguous per lane; a, y0 [lanes, na]; the carried
+// state is s[j] = y_{t-1-j} (newest first), which is also the layout of y0.
+//
+// One warp owns one lane and walks its sequence in tiles of 512 steps, 16 consecutive steps per
+// thread.  The recurrence is linear in (state, input), so a 16-step segment maps its start state
+// to its end state as s' = M s + r with M = (companion matrix)^16 the same for every segment and
+// r the segment's zero-state response.  Per tile:
+//   1. each thread runs its 16 steps from a zero state (registers) to get r,
+//   2. a warp-shuffle Kogge-Stone scan over the 32 segments composes the affine maps; step d
+//      uses M^(2^d), and the carry from the previous tile enters through thread 0,
+//   3. each thread re-runs its 16 steps from its true start state and the tile is stored.
+// The five powers M^(1,2,4,8,16) are built once per lane at kernel start in float64 (repeated
+// squaring) and kept in shared memory as float32, clamped to +-FLT_MAX so that 0 * overflow
+// stays 0 instead of becoming NaN; an unstable filter still runs to inf like the sequential loop.
+//
+// Memory pipeline: every warp keeps S-1 tiles in flight in a private shared-memory ring filled by
+// coalesced 16-byte cp.async (4-byte when L or a pointer is not 16-byte aligned); chunks are
+// padded to 80 bytes so that the per-thread 64-byte reads are bank-conflict free.  Results go
+// back through the same buffer and leave as coalesced 16-byte stores.  No workspace, no atomics:
+// the adjoint's grad_a is accumulated per thread in registers across all tiles and reduced with
+// a fixed butterfly at the end, so results are bitwise reproducible.
+#include <float.h>
+
+#include "common.cuh"
+
+namespace b200 {
+
+struct AllpoleArgs {
+    const float* a;    // [lanes, na]
+    const float* in;   // fwd: w        bwd: g
+    const float* yin;  // bwd: forward output y
+    const float* y0;   // may be null
+    float* out;        // fwd: y        bwd: gw
+    float* ga;         // bwd: [lanes, na]
+    float* gy0;        // bwd: [lanes, na] or null
+    long long lanes, L;
+};
+
+constexpr int kSeg = 16;            // steps per thread
+constexpr int kTile = 32 * kSeg;    // steps per warp tile
+constexpr int kChunk = kSeg + 4;    // floats per thread chunk in shared memory (80 bytes)
+constexpr int kStageF = 32 * kChunk;  // floats per staged tensor tile
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
+    const unsigned int d = static_cast<unsigned int>(__cvta_generic_to_shared(smem_dst));
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async4(void* smem_dst, const void* gsrc) {
+    const unsigned int d = static_cast<unsigned int>(__cvta_generic_to_shared(smem_dst));
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+__device__ __forceinline__ float clamp_finite(double x) {
+    if (x > (double)FLT_MAX) return FLT_MAX;
+    if (x < -(double)FLT_MAX) return -FLT_MAX;
+    return (float)x;  // NaN passes through
+}
+
+// One recurrence step on the shift-register state: returns y = in - a.s and shifts y in.
+template <int NA>
+__device__ __forceinline__ float iir_step(const float (&a)[NA], float (&s)[NA], float in) {
+    float acc = 0.f;
+#pragma unroll
+    for (int j = NA - 1; j >= 1; --j) acc = fmaf(a[j], s[j], acc);  // older taps first:
+    const float y = in - fmaf(a[0], s[0], acc);                   // only a_1 y_{t-1} is on the critical path
+#pragma unroll
+    for (int j = NA - 1; j >= 1; --j) s[j] = s[j - 1];
+    s[0] = y;
+    return y;
+}
+
+template <int NA, bool BWD, int VEC, int W, int S>
+__global__ void __launch_bounds__(32 * W) allpole_kernel(const AllpoleArgs p) {
+    static_assert(VEC == 4 || VEC == 1, "pieces are 16 or 4 bytes");
+    constexpr int NTENS = BWD ? 2 : 1;
+    constexpr int PIECES = kTile / VEC;  // copy pieces per tile and tensor
+    constexpr int PPC = kSeg / VEC;      // pieces per thread chunk
+
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int w = threadIdx.x >> 5;
+    const int lid = threadIdx.x & 31;
+    const long long lane = (long long)blockIdx.x * W + w;
+    if (lane >= p.lanes) return;  // warps never synchronise with each other
+
+    double* Md = reinterpret_cast<double*>(smem_raw) + w * (2 * NA * NA);                          // squaring scratch
+    float* fbase = reinterpret_cast<float*>(reinterpret_cast<double*>(smem_raw) + W * (2 * NA * NA));
+    float* ring = fbase + w * (S * NTENS * kStageF);                                              // [S][NTENS][32][kChunk]
+    float* Mf = fbase + W * (S * NTENS * kStageF) + w * (5 * NA * NA);                            // M^(2^d), d = 0..4
+
+    const long long L = p.L;
+    const long long C = (L + kTile - 1) / kTile;
+    const float* in = p.in + lane * L;
+    const float* yin = BWD ? p.yin + lane * L : nullptr;
+    float* out = p.out + lane * L;
+
+    float a[NA];
+#pragma unroll
+    for (int j = 0; j < NA; ++j) a[j] = p.a[lane * NA + j];
+
+    auto phys0_of = [&](long long c) -> long long { return BWD ? (L - (c + 1) * kTile) : c * kTile; };
+    auto issue = [&](long long c, int slot) {
+        const long long ph = phys0_of(c);
+        float* dst = ring + slot * (NTENS * kStageF);
+#pragma unroll
+        for (int q = 0; q < PIECES / 32; ++q) {
+            const int gidx = q * 32 + lid;
+            const long long t = ph + (long long)gidx * VEC;
+            if (t >= 0 && t < L) {
+                float* d = dst + (gidx / PPC) * kChunk + (gidx % PPC) * VEC;
+                if constexpr (VEC == 4) {
+                    cp_async16(d, in + t);
+                    if constexpr (BWD) cp_async16(d + kStageF, yin + t);
+                } else {
+                    cp_async4(d, in + t);
+                    if constexpr (BWD) cp_async4(d + kStageF, yin + t);
+                }
+            }
+        }
+    };
+
+#pragma unroll
+    for (int q = 0; q < S - 1; ++q) {
+        if (q < C) issue(q, q);
+        cp_commit();
+    }
+
+    // ---------------------------------------------------------------- M = companion^16 and its powers
+    if (lid < NA) {
+        double s[NA];
+#pragma unroll
+        for (int j = 0; j < NA; ++j) s[j] = (j == lid) ? 1.0 : 0.0;
+        for (int t = 0; t < kSeg; ++t) {
+            double acc = 0.0;
+#pragma unroll
+            for (int j = 0; j < NA; ++j) acc += (double)a[j] * s[j];
+#pragma unroll
+            for (int j = NA - 1; j >= 1; --j) s[j] = s[j - 1];
+            s[0] = -acc;
+        }
+#pragma unroll
+        for (int i = 0; i < NA; ++i) Md[i * NA + lid] = s[i];  // column `lid`
+    }
+    __syncwarp();
+    {
+        int cur = 0;
+        for (int d = 0; d < 5; ++d) {
+            const double* src = Md + cur * NA * NA;
+            double* dst = Md + (cur ^ 1) * NA * NA;
+            for (int e = lid; e < NA * NA; e += 32) {
+                Mf[d * NA * NA + e] = clamp_finite(src[e]);
+                if (d < 4) {
+                    const int i = e / NA, j = e % NA;
+                    double acc = 0.0;
+                    for (int k = 0; k < NA; ++k) acc += src[i * NA + k] * src[k * NA + j];
+                    dst[e] = acc;
+                }
+            }
+            __syncwarp();
+            cur ^= 1;
+        }
+    }
+
+    float cin[NA], acc_a[NA];
+#pragma unroll
+    for (int j = 0; j < NA; ++j) {
+        cin[j] = (!BWD && p.y0 != nullptr) ? p.y0[lane * NA + j] : 0.f;
+        acc_a[j] = 0.f;
+    }
+    const int ch = BWD ? 31 - lid : lid;  // this thread's chunk, in physical order
+
+    for (long long c = 0; c < C; ++c) {
+        const int slot = (int)(c % S);
+        const long long ph = phys0_of(c);
+        float* stage = ring + slot * (NTENS * kStageF);
+        cp_wait<S - 2>();
+        __syncwarp();
+
+        float v[kSeg], yv[BWD ? kSeg : 1];
+        const long long tbase = ph + ch * kSeg;
+#pragma unroll
+        for (int q = 0; q < kSeg / 4; ++q) {
+            const float4 t4 = *reinterpret_cast<const float4*>(stage + ch * kChunk + 4 * q);
+            v[4 * q] = t4.x, v[4 * q + 1] = t4.y, v[4 * q + 2] = t4.z, v[4 * q + 3] = t4.w;
+            if constexpr (BWD) {
+                const float4 u4 = *reinterpret_cast<const float4*>(stage + kStageF + ch * kChunk + 4 * q);
+                yv[4 * q] = u4.x, yv[4 * q + 1] = u4.y, yv[4 * q + 2] = u4.z, yv[4 * q + 3] = u4.w;
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < kSeg; ++r) {  // steps outside the sequence: zero input, never stored
+            const bool okr = (tbase + r) >= 0 && (tbase + r) < L;
+            if (!okr) {
+                v[r] = 0.f;
+                if constexpr (BWD) yv[r] = 0.f;
+            }
+        }
+        __syncwarp();  // everyone has read this stage before the next tile's copies may land in it
+        if (c + S - 1 < C) issue(c + S - 1, (int)((c + S - 1) % S));
+        cp_commit();
+
+        // 1. zero-state response of this thread's segment
+        float s[NA];
+#pragma unroll
+        for (int j = 0; j < NA; ++j) s[j] = 0.f;
+#pragma unroll
+        for (int k = 0; k < kSeg; ++k) iir_step<NA>(a, s, v[BWD ? kSeg - 1 - k : k]);
+
+        // 2. carry of the previous tile enters at thread 0; Kogge-Stone over the 32 segments
+        if (lid == 0) {
+#pragma unroll
+            for (int i = 0; i < NA; ++i) {
+                float t = s[i];
+#pragma unroll
+                for (int j = 0; j < NA; ++j) t = fmaf(Mf[i * NA + j], cin[j], t);
+                s[i] = t;
+            }
+        }
+#pragma unroll
+        for (int d = 0; d < 5; ++d) {
+            float sp[NA];
+#pragma unroll
+            for (int j = 0; j < NA; ++j) sp[j] = __shfl_up_sync(0xffffffffu, s[j], 1 << d);
+            if (lid >= (1 << d)) {
+                const float* M = Mf + d * NA * NA;
+#pragma unroll
+                for (int i = 0; i < NA; ++i) {
+                    float t = s[i];
+#pragma unroll
+                    for (int j = 0; j < NA; ++j) t = fmaf(M[i * NA + j], sp[j], t);
+                    s[i] = t;
+                }
+            }
+        }
+        float st[NA];
+#pragma unroll
+        for (int j = 0; j < NA; ++j) {
+            const float up = __shfl_up_sync(0xffffffffu, s[j], 1);
+            st[j] = lid == 0 ? cin[j] : up;
+        }
+#pragma unroll
+        for (int j = 0; j < NA; ++j) cin[j] = __shfl_sync(0xffffffffu, s[j], 31);
+
+        // 3. the true run of this segment
+#pragma unroll
+        for (int k = 0; k < kSeg; ++k) {
+            const int r = BWD ? kSeg - 1 - k : k;
+            if constexpr (BWD) {  // grad_a_k += G_{t+1+k} * y_t with the state BEFORE the step
+#pragma unroll
+                for (int j = 0; j < NA; ++j) acc_a[j] = fmaf(st[j], yv[r], acc_a[j]);
+            }
+            v[r] = iir_step<NA>(a, st, v[r]);
+        }
+
+        // stage the results in this thread's chunk and store the tile coalesced
+#pragma unroll
+        for (int q = 0; q < kSeg / 4; ++q)
+            *reinterpret_cast<float4*>(stage + ch * kChunk + 4 * q) =
+                make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+        __syncwarp();
+#pragma unroll
+        for (int q = 0; q < PIECES / 32; ++q) {
+            const int gidx = q * 32 + lid;
+            const long long t = ph + (long long)gidx * VEC;
+            if (t >= 0 && t < L) {
+                const float* sp = stage + (gidx / PPC) * kChunk + (gidx % PPC) * VEC;
+                if constexpr (VEC == 4) {
+                    __stcs(reinterpret_cast<float4*>(out + t), *reinterpret_cast<const float4*>(sp));
+                } else {
+                    __stcs(out + t, *sp);
+                }
+            }
+        }
+        __syncwarp();
+    }
+    cp_wait<0>();
+
+    if constexpr (BWD) {
+        // grad_a: fixed butterfly over the warp, then the initial-state terms from G_0..G_{na-1}
+#pragma unroll
+        for (int j = 0; j < NA; ++j) {
+#pragma unroll
+            for (int off = 16; off >= 1; off >>= 1) acc_a[j] += __shfl_xor_sync(0xffffffffu, acc_a[j], off);
+        }
+        __syncwarp();
+        if (lid == 0) {
+            float G[NA];
+#pragma unroll
+            for (int q = 0; q < NA; ++q) G[q] = q < L ? __ldcg(out + q) : 0.f;
+#pragma unroll
+            for (int i = 1; i <= NA; ++i) {
+                float t = acc_a[i - 1];
+                if (p.y0 != nullptr) {
+#pragma unroll
+                    for (int k = 1; k <= NA; ++k)
+                        if (k <= i) t = fmaf(G[i - k], p.y0[lane * NA + k - 1], t);
+                }
+                p.ga[lane * NA + i - 1] = -t;
+            }
+            if (p.gy0 != nullptr) {
+#pragma unroll
+                for (int j = 0; j < NA; ++j) {
+                    float t = 0.f;
+#pragma unroll
+                    for (int i = 1; i <= NA; ++i)
+                        if (i >= j + 1) t = fmaf(a[i - 1], G[i - 1 - j], t);
+                    p.gy0[lane * NA + j] = -t;
+                }
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------- host side
+#ifndef ALLPOLE_W
+#define ALLPOLE_W 4  // lanes (warps) per CTA
+#endif
+#ifndef ALLPOLE_FWD_S
+#define ALLPOLE_FWD_S 6  // ring stages per warp
+#endif
+#ifndef ALLPOLE_BWD_S
+#define ALLPOLE_BWD_S 4
+#endif
+
+template <int NA, bool BWD, int VEC>
+static int launch_allpole(const AllpoleArgs& a, cudaStream_t st) {
+    constexpr int W = ALLPOLE_W;
+    constexpr int S = BWD ? ALLPOLE_BWD_S : ALLPOLE_FWD_S;
+    constexpr int NTENS = BWD ? 2 : 1;
+    constexpr size_t smem = (size_t)W * (2 * NA * NA * sizeof(double) + (size_t)S * NTENS * kStageF * sizeof(float) +
+                                         5 * NA * NA * sizeof(float));
+    auto kern = allpole_kernel<NA, BWD, VEC, W, S>;
+    static bool configured[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return B200_ERR_LAUNCH;
+        configured[dev] = true;
+    }
+    const long long grid = (a.lanes + W - 1) / W;
+    if (grid > 0x7fffffffLL) return B200_ERR_UNSUPPORTED;
+    kern<<<(unsigned int)grid, 32 * W, smem, st>>>(a);
+    return cudaGetLastError() == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
+}
+
+template <bool BWD, int VEC>
+static int dispatch_na(int na, const AllpoleArgs& a, cudaStream_t st) {
+    switch (na) {
+#define B200_NA_CASE(n) \
+    case n:             \
+        return launch_allpole<n, BWD, VEC>(a, st);
+        B200_NA_CASE(1) B200_NA_CASE(2) B200_NA_CASE(3) B200_NA_CASE(4) B200_NA_CASE(5) B200_NA_CASE(6)
+        B200_NA_CASE(7) B200_NA_CASE(8) B200_NA_CASE(9) B200_NA_CASE(10) B200_NA_CASE(11) B200_NA_CASE(12)
+        B200_NA_CASE(13) B200_NA_CASE(14) B200_NA_CASE(15) B200_NA_CASE(16)
+#undef B200_NA_CASE
+        default:
+            return B200_ERR_UNSUPPORTED;
+    }
+}
+
+static int run_allpole(bool bwd, long long lanes, long long L, long long na, const void* a, const void* in,
+                       const void* yin, const void* y0, void* out, void* ga, void* gy0, void* stream) {
+    if (lanes < 0 || L < 0 || na < 1) return B200_ERR_ARG;
+    if (na > 16) return B200_ERR_UNSUPPORTED;
+    if (lanes == 0) return B200_OK;
+    if (!a || (bwd && !ga)) return B200_ERR_ARG;
+    if (L > 0 && (!in || !out || (bwd && !yin))) return B200_ERR_ARG;
+    if (bwd && y0 && !gy0) return B200_ERR_ARG;
+    const uintptr_t por = (uintptr_t)a | (uintptr_t)in | (uintptr_t)yin | (uintptr_t)y0 | (uintptr_t)out |
+                          (uintptr_t)ga | (uintptr_t)gy0;
+    if (por % 4 != 0) return B200_ERR_ARG;
+    AllpoleArgs p;
+    p.a = static_cast<const float*>(a);
+    p.in = static_cast<const float*>(in);
+    p.yin = static_cast<const float*>(yin);
+    p.y0 = static_cast<const float*>(y0);
+    p.out = static_cast<float*>(out);
+    p.ga = static_cast<float*>(ga);
+    p.gy0 = y0 ? static_cast<float*>(gy0) : nullptr;
+    p.lanes = lanes;
+    p.L = L;
+    const uintptr_t seq_or = (uintptr_t)in | (uintptr_t)yin | (uintptr_t)out;
+    const bool vec = (L % 4 == 0) && (seq_or % 16 == 0);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (bwd) return vec ? dispatch_na<true, 4>((int)na, p, st) : dispatch_na<true, 1>((int)na, p, st);
+    return vec ? dispatch_na<false, 4>((int)na, p, st) : dispatch_na<false, 1>((int)na, p, st);
+}
+
+}  // namespace b200
+
+extern "C" {
+
+int b200_allpole_fwd(int64_t lanes, int64_t L, int64_t na, const void* a, const void* w, const void* y0,
+                     void* y, void* stream) {
+    return b200::run_allpole(false, lanes, L, na, a, w, nullptr, y0, y, nullptr, nullptr, stream);
+}
+
+int b200_allpole_bwd(int64_t lanes, int64_t L, int64_t na, const void* g, const void* a, const void* y,
+                     const void* y0, void* ga, void* gw, void* gy0, void* stream) {
+    return b200::run_allpole(true, lanes, L, na, a, g, y, y0, gw, ga, gy0, stream);
+}
+
+}  // extern "C"
