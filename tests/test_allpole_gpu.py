@@ -177,8 +177,10 @@ def test_config4_full_size_properties():
             pred -= a[:, k : k + 1] * o[:, 3 - k : L - 1 - k]
         return (o[:, 4:] - pred).abs().max().item()
 
-    assert residual(y, w, False) < 2e-5 * y.abs().max().item()
+    # a state error e at a segment seam shows up as a residual of about sum|a_k| * e
+    amp = 1.0 + a.abs().sum(1).max().item()
+    assert residual(y, w, False) < 1e-5 * amp * y.abs().max().item()
     g = torch.randn(Bn * P, L, device="cuda", generator=gen)
     ga, gw, _ = ap._allpole_bwd_op(g, a, y, None)
-    assert residual(gw, g, True) < 2e-5 * gw.abs().max().item()
+    assert residual(gw, g, True) < 1e-5 * amp * gw.abs().max().item()
     assert torch.isfinite(ga).all()

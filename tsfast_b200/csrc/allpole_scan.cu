@@ -12,9 +12,12 @@
 //   2. a warp-shuffle Kogge-Stone scan over the 32 segments composes the affine maps; step d
 //      uses M^(2^d), and the carry from the previous tile enters through thread 0,
 //   3. each thread re-runs its 16 steps from its true start state and the tile is stored.
-// The five powers M^(1,2,4,8,16) are built once per lane at kernel start in float64 (repeated
-// squaring) and kept in shared memory as float32, clamped to +-FLT_MAX so that 0 * overflow
-// stays 0 instead of becoming NaN; an unstable filter still runs to inf like the sequential loop.
+// The five powers M^(1,2,4,8,16) are built once per lane at kernel start by repeated squaring and
+// kept in shared memory.  Powers and the composition of segment states are float64: with poles
+// near the unit circle M has large entries that cancel, and a float32 composition loses ten times
+// the accuracy of the sequential float32 loop, while float64 matches it (steps 1 and 3, i.e. all
+// per-element work, stay float32).  Entries are clamped to +-1e300 so that 0 * overflow stays 0
+// instead of becoming NaN; an unstable filter still runs to inf like the sequential loop.
 //
 // Memory pipeline: every warp keeps S-1 tiles in flight in a private shared-memory ring filled by
 // coalesced 16-byte cp.async (4-byte when L or a pointer is not 16-byte aligned); chunks are
@@ -58,10 +61,10 @@ __device__ __forceinline__ void cp_wait() {
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
-__device__ __forceinline__ float clamp_finite(double x) {
-    if (x > (double)FLT_MAX) return FLT_MAX;
-    if (x < -(double)FLT_MAX) return -FLT_MAX;
-    return (float)x;  // NaN passes through
+__device__ __forceinline__ double clamp_finite(double x) {
+    if (x > 1e300) return 1e300;
+    if (x < -1e300) return -1e300;
+    return x;  // NaN passes through
 }
 
 // One recurrence step on the shift-register state: returns y = in - a.s and shifts y in.
@@ -90,10 +93,10 @@ __global__ void __launch_bounds__(32 * W) allpole_kernel(const AllpoleArgs p) {
     const long long lane = (long long)blockIdx.x * W + w;
     if (lane >= p.lanes) return;  // warps never synchronise with each other
 
-    double* Md = reinterpret_cast<double*>(smem_raw) + w * (2 * NA * NA);                          // squaring scratch
-    float* fbase = reinterpret_cast<float*>(reinterpret_cast<double*>(smem_raw) + W * (2 * NA * NA));
-    float* ring = fbase + w * (S * NTENS * kStageF);                                              // [S][NTENS][32][kChunk]
-    float* Mf = fbase + W * (S * NTENS * kStageF) + w * (5 * NA * NA);                            // M^(2^d), d = 0..4
+    double* Md = reinterpret_cast<double*>(smem_raw) + w * (7 * NA * NA);  // squaring scratch (2 matrices)
+    double* Mp = Md + 2 * NA * NA;                                           // M^(2^d), d = 0..4
+    float* ring = reinterpret_cast<float*>(reinterpret_cast<double*>(smem_raw) + W * (7 * NA * NA)) +
+                  w * (S * NTENS * kStageF);  // [S][NTENS][32][kChunk]
 
     const long long L = p.L;
     const long long C = (L + kTile - 1) / kTile;
@@ -155,7 +158,7 @@ __global__ void __launch_bounds__(32 * W) allpole_kernel(const AllpoleArgs p) {
             const double* src = Md + cur * NA * NA;
             double* dst = Md + (cur ^ 1) * NA * NA;
             for (int e = lid; e < NA * NA; e += 32) {
-                Mf[d * NA * NA + e] = clamp_finite(src[e]);
+                Mp[d * NA * NA + e] = clamp_finite(src[e]);
                 if (d < 4) {
                     const int i = e / NA, j = e % NA;
                     double acc = 0.0;
@@ -168,10 +171,11 @@ __global__ void __launch_bounds__(32 * W) allpole_kernel(const AllpoleArgs p) {
         }
     }
 
-    float cin[NA], acc_a[NA];
+    double cin[NA];  // state carried into the current tile
+    float acc_a[NA];
 #pragma unroll
     for (int j = 0; j < NA; ++j) {
-        cin[j] = (!BWD && p.y0 != nullptr) ? p.y0[lane * NA + j] : 0.f;
+        cin[j] = (!BWD && p.y0 != nullptr) ? (double)p.y0[lane * NA + j] : 0.0;
         acc_a[j] = 0.f;
     }
     const int ch = BWD ? 31 - lid : lid;  // this thread's chunk, in physical order
@@ -213,40 +217,43 @@ __global__ void __launch_bounds__(32 * W) allpole_kernel(const AllpoleArgs p) {
 #pragma unroll
         for (int k = 0; k < kSeg; ++k) iir_step<NA>(a, s, v[BWD ? kSeg - 1 - k : k]);
 
-        // 2. carry of the previous tile enters at thread 0; Kogge-Stone over the 32 segments
+        // 2. carry of the previous tile enters at thread 0; Kogge-Stone over the 32 segments (float64)
+        double sd[NA];
+#pragma unroll
+        for (int j = 0; j < NA; ++j) sd[j] = (double)s[j];
         if (lid == 0) {
 #pragma unroll
             for (int i = 0; i < NA; ++i) {
-                float t = s[i];
+                double t = sd[i];
 #pragma unroll
-                for (int j = 0; j < NA; ++j) t = fmaf(Mf[i * NA + j], cin[j], t);
-                s[i] = t;
+                for (int j = 0; j < NA; ++j) t = fma(Mp[i * NA + j], cin[j], t);
+                sd[i] = t;
             }
         }
 #pragma unroll
         for (int d = 0; d < 5; ++d) {
-            float sp[NA];
+            double sp[NA];
 #pragma unroll
-            for (int j = 0; j < NA; ++j) sp[j] = __shfl_up_sync(0xffffffffu, s[j], 1 << d);
+            for (int j = 0; j < NA; ++j) sp[j] = __shfl_up_sync(0xffffffffu, sd[j], 1 << d);
             if (lid >= (1 << d)) {
-                const float* M = Mf + d * NA * NA;
+                const double* M = Mp + d * NA * NA;
 #pragma unroll
                 for (int i = 0; i < NA; ++i) {
-                    float t = s[i];
+                    double t = sd[i];
 #pragma unroll
-                    for (int j = 0; j < NA; ++j) t = fmaf(M[i * NA + j], sp[j], t);
-                    s[i] = t;
+                    for (int j = 0; j < NA; ++j) t = fma(M[i * NA + j], sp[j], t);
+                    sd[i] = t;
                 }
             }
         }
         float st[NA];
 #pragma unroll
         for (int j = 0; j < NA; ++j) {
-            const float up = __shfl_up_sync(0xffffffffu, s[j], 1);
-            st[j] = lid == 0 ? cin[j] : up;
+            const double up = __shfl_up_sync(0xffffffffu, sd[j], 1);
+            st[j] = (float)(lid == 0 ? cin[j] : up);
         }
 #pragma unroll
-        for (int j = 0; j < NA; ++j) cin[j] = __shfl_sync(0xffffffffu, s[j], 31);
+        for (int j = 0; j < NA; ++j) cin[j] = __shfl_sync(0xffffffffu, sd[j], 31);
 
         // 3. the true run of this segment
 #pragma unroll
@@ -334,8 +341,7 @@ static int launch_allpole(const AllpoleArgs& a, cudaStream_t st) {
     constexpr int W = ALLPOLE_W;
     constexpr int S = BWD ? ALLPOLE_BWD_S : ALLPOLE_FWD_S;
     constexpr int NTENS = BWD ? 2 : 1;
-    constexpr size_t smem = (size_t)W * (2 * NA * NA * sizeof(double) + (size_t)S * NTENS * kStageF * sizeof(float) +
-                                         5 * NA * NA * sizeof(float));
+    constexpr size_t smem = (size_t)W * (7 * NA * NA * sizeof(double) + (size_t)S * NTENS * kStageF * sizeof(float));
     auto kern = allpole_kernel<NA, BWD, VEC, W, S>;
     static bool configured[64] = {false};
     int dev = 0;
