@@ -80,6 +80,28 @@ int b200_allpole_fwd(int64_t lanes, int64_t L, int64_t na, const void* a, const 
 int b200_allpole_bwd(int64_t lanes, int64_t L, int64_t na, const void* g, const void* a, const void* y,
                      const void* y0, void* ga, void* gw, void* gy0, void* stream);
 
+/* ---- S3: fused Mamba selective-scan section ---------------------------------------------
+ * delta = softplus(draw) (threshold 20); h_t = exp(delta_t A) h_{t-1} + delta_t u_t B_t;
+ * out_t = (h_t . C_t + Dp u_t) * z_t * sigmoid(z_t); hlast = h_L.  All float32.
+ * draw, u, z, out [B,L,D]; A [D,N]; Bt, Ct [B,L,N]; Dp [D]; h0, hlast [B,D,N] (h0 may be NULL);
+ * 1 <= N <= 128.  Replaces mamba_fwd / mamba_bwd of tsfast/models/architectures/mamba/
+ * backend_c.py:106-245 (CPU C ABI) and _mamba_fwd / _mamba_bwd of mamba/mamba_triton.py:85-286,
+ * i.e. the bodies of tsfast::mamba_scan, mamba_scan_train and mamba_scan_bwd.
+ * chk: state checkpoints [B, ceil(L / b200_mamba_chk_interval()), D, N] written by the forward
+ * for the backward (slot k = state after step (k+1)*interval - 1); pass NULL for inference.
+ * Backward: gout [B,L,D] upstream gradient, ghlast [B,D,N] or NULL (zero); writes gdraw, gu, gz
+ * [B,L,D], gA [D,N], gBt, gCt [B,L,N], gDp [D] and, when h0 != NULL, gh0 [B,D,N].  Sums over
+ * channels and batch go through partial buffers in the workspace, added in a fixed order. */
+int b200_mamba_chk_interval(void);
+int b200_mamba_fwd(int64_t B, int64_t L, int64_t D, int64_t N, const void* draw, const void* A, const void* Bt,
+                   const void* Ct, const void* u, const void* z, const void* Dp, const void* h0, void* out,
+                   void* hlast, void* chk, void* stream);
+size_t b200_mamba_bwd_workspace_bytes(int64_t B, int64_t L, int64_t D, int64_t N);
+int b200_mamba_bwd(int64_t B, int64_t L, int64_t D, int64_t N, const void* draw, const void* A, const void* Bt,
+                   const void* Ct, const void* u, const void* z, const void* Dp, const void* h0, const void* chk,
+                   const void* gout, const void* ghlast, void* gdraw, void* gA, void* gBt, void* gCt, void* gu,
+                   void* gz, void* gDp, void* gh0, void* workspace, size_t workspace_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

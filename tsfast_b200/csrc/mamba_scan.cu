@@ -1,0 +1,688 @@
+// Fused Mamba selective-scan section (S3), float32, forward and adjoint:
+//   delta = softplus(draw);  h_t = exp(delta_t A) h_{t-1} + delta_t u_t B_t;
+//   out_t = (h_t . C_t + Dp u_t) * z_t * sigmoid(z_t);  h_last = h_L.
+// draw, u, z, out [B, L, D] (channel axis contiguous); A [D, N]; Bt, Ct [B, L, N]; Dp [D];
+// h0, h_last [B, D, N].  Nothing [B, L, D, N]-sized ever touches HBM.
+//
+// Work split: one CTA owns one batch row and a block of DB channels for the whole sequence and
+// walks time in tiles of kT steps.  A thread owns one channel and 4 of its N states (TPC threads
+// per channel, neighbouring lanes), keeps them in registers and steps through time
+// sequentially: the scan costs ONE exp per state and step, which is what bounds this kernel (the
+// special-function unit, not HBM), so time is not split across threads (that would double the
+// exps).  Per tile the raw inputs arrive through a cp.async ring (S-1 tiles in flight, every row
+// a coalesced 128-byte segment), a cooperative pass turns draw into delta and z into the SiLU
+// gate once per (t, d), then the state loop runs from shared memory and the gated outputs leave
+// through a staging tile as coalesced 16-byte stores.
+//
+// Training: the forward also writes the state every kT steps (chk [B, ceil(L/kT), D, N], slot k =
+// state after step (k+1)*kT - 1), 1/16 of a full state store.  The adjoint walks the tiles in
+// reverse: it recomputes the tile's states and decays from the checkpoint into shared memory
+// (one exp per state and step again), then sweeps the tile backwards running
+// G_t = gy_t C_t + lam_{t+1} G_{t+1}.  Reductions over channels (grad_B, grad_C) are done in
+// registers with a fixed reduce-scatter butterfly, across warps through shared memory and across
+// channel blocks / batch rows through partial buffers summed in a fixed order: no atomics, so
+// results are bitwise reproducible.
+#include <initializer_list>
+
+#include "common.cuh"
+
+namespace b200 {
+
+constexpr int kT = 16;       // steps per tile == checkpoint interval
+constexpr int kNPT = 4;      // states per thread
+constexpr float kLog2e = 1.4426950408889634f;
+
+struct MambaArgs {
+    const float *draw, *A, *Bt, *Ct, *u, *z, *Dp, *h0;
+    float *out, *chk, *hlast;
+    // adjoint only
+    const float *gout, *ghlast;
+    float *gdraw, *gu, *gz, *gh0;
+    float *gA_part, *gDp_part, *gB_part, *gC_part;  // [B,D,N], [B,D], [ndb,B,L,N] x2
+    long long B, L, D, N;
+    long long ndb, NC;  // channel blocks per row, tiles per sequence
+};
+
+__device__ __forceinline__ void mcp16(void* smem_dst, const void* gsrc) {
+    const unsigned int d = static_cast<unsigned int>(__cvta_generic_to_shared(smem_dst));
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void mcp4(void* smem_dst, const void* gsrc) {
+    const unsigned int d = static_cast<unsigned int>(__cvta_generic_to_shared(smem_dst));
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void mcp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void mcp_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+__device__ __forceinline__ float ex2_fast(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+// softplus with PyTorch's threshold (x > 20 -> x)
+__device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(__expf(x)); }
+__device__ __forceinline__ float sigmoid_f(float x) { return __fdividef(1.f, 1.f + __expf(-x)); }
+
+// Copy a [rows x cols] float block (row pitch `pitch` in global memory, rows below `rows_live`
+// and columns below `cols_live` only) into a dense [rows x ld] shared tile, cooperatively.
+// VEC = 4 needs 16-byte aligned rows in both places and cols_live % 4 == 0.
+template <int VEC, int NTHR>
+__device__ __forceinline__ void copy_tile(float* dst, int ld, const float* src, long long pitch, int rows_live,
+                                          int cols, int cols_live, int tid) {
+    const int ppr = cols / VEC;  // pieces per row
+    for (int e = tid; e < rows_live * ppr; e += NTHR) {
+        const int r = e / ppr, c = (e - r * ppr) * VEC;
+        if (c < cols_live) {
+            if constexpr (VEC == 4) {
+                mcp16(dst + r * ld + c, src + r * pitch + c);
+            } else {
+                mcp4(dst + r * ld + c, src + r * pitch + c);
+            }
+        }
+    }
+}
+
+// ================================================================================ forward
+template <int TPC, int DB, bool STORE_CHK, int VEC, int S>
+__global__ void __launch_bounds__(DB* TPC) mamba_fwd_kernel(const MambaArgs p) {
+    constexpr int NTHR = DB * TPC;
+    constexpr int NPAD = kNPT * TPC;
+    constexpr int STAGE = 3 * kT * DB + 2 * kT * NPAD;  // floats per ring stage
+    extern __shared__ __align__(16) float smem[];
+    float* ring = smem;                  // [S][STAGE]
+    float* outbuf = smem + S * STAGE;    // [2][kT][DB]
+
+    const int tid = threadIdx.x;
+    const int dl = tid / TPC, ng = tid % TPC;
+    const long long b = blockIdx.x / p.ndb;
+    const long long d0 = (blockIdx.x - b * p.ndb) * DB;
+    const long long d = d0 + dl;
+    const int n0 = ng * kNPT;
+    const long long L = p.L, D = p.D, N = p.N;
+    const bool d_ok = d < D;
+    const int dcols = (int)((D - d0) < DB ? (D - d0) : DB);
+
+    for (int e = tid; e < S * STAGE + 2 * kT * DB; e += NTHR) smem[e] = 0.f;  // pads must read as zero
+    __syncthreads();
+
+    auto issue = [&](long long c, int slot) {
+        const long long t0 = c * kT;
+        const int rows = (int)((L - t0) < kT ? (L - t0) : kT);
+        float* st = ring + slot * STAGE;
+        const long long off = (b * L + t0) * D + d0;
+        copy_tile<VEC, NTHR>(st, DB, p.draw + off, D, rows, DB, dcols, tid);
+        copy_tile<VEC, NTHR>(st + kT * DB, DB, p.u + off, D, rows, DB, dcols, tid);
+        copy_tile<VEC, NTHR>(st + 2 * kT * DB, DB, p.z + off, D, rows, DB, dcols, tid);
+        const long long offn = (b * L + t0) * N;
+        copy_tile<VEC, NTHR>(st + 3 * kT * DB, NPAD, p.Bt + offn, N, rows, NPAD, (int)N, tid);
+        copy_tile<VEC, NTHR>(st + 3 * kT * DB + kT * NPAD, NPAD, p.Ct + offn, N, rows, NPAD, (int)N, tid);
+    };
+    auto store_out = [&](long long c) {  // staged gated outputs of tile c -> global, coalesced
+        const long long t0 = c * kT;
+        const int rows = (int)((L - t0) < kT ? (L - t0) : kT);
+        const float* ob = outbuf + (c & 1) * kT * DB;
+        float* dst = p.out + (b * L + t0) * D + d0;
+        constexpr int PPR = DB / VEC;
+        for (int e = tid; e < rows * PPR; e += NTHR) {
+            const int r = e / PPR, cc = (e - r * PPR) * VEC;
+            if (cc < dcols) {
+                if constexpr (VEC == 4) {
+                    __stcs(reinterpret_cast<float4*>(dst + r * D + cc), *reinterpret_cast<const float4*>(ob + r * DB + cc));
+                } else {
+                    __stcs(dst + r * D + cc, ob[r * DB + cc]);
+                }
+            }
+        }
+    };
+
+#pragma unroll
+    for (int q = 0; q < S - 1; ++q) {
+        if (q < p.NC) issue(q, q);
+        mcp_commit();
+    }
+
+    float A2[kNPT], h[kNPT];
+#pragma unroll
+    for (int q = 0; q < kNPT; ++q) {
+        const bool ok = d_ok && (n0 + q) < N;
+        A2[q] = ok ? p.A[d * N + n0 + q] * kLog2e : 0.f;
+        h[q] = (ok && p.h0 != nullptr) ? p.h0[(b * D + d) * N + n0 + q] : 0.f;
+    }
+    const float Dp = d_ok ? p.Dp[d] : 0.f;
+
+    for (long long c = 0; c < p.NC; ++c) {
+        const int slot = (int)(c % S);
+        float* st = ring + slot * STAGE;
+        const int tlive = (int)((L - c * kT) < kT ? (L - c * kT) : kT);
+        mcp_wait<S - 2>();
+        __syncthreads();  // tile c has landed for everyone; tile c-1 is fully consumed and staged
+        if (c + S - 1 < p.NC) issue(c + S - 1, (int)((c + S - 1) % S));
+        mcp_commit();
+        if (c > 0) store_out(c - 1);
+
+        // once per (t, d): draw -> delta, z -> z * sigmoid(z)
+        for (int e = tid; e < tlive * DB; e += NTHR) {
+            st[e] = softplus_f(st[e]);
+            const float zz = st[2 * kT * DB + e];
+            st[2 * kT * DB + e] = zz * sigmoid_f(zz);
+        }
+        __syncthreads();
+
+        float* ob = outbuf + (c & 1) * kT * DB;
+        const float* Bs = st + 3 * kT * DB + n0;
+        const float* Cs = Bs + kT * NPAD;
+        for (int t = 0; t < tlive; ++t) {
+            const float delta = st[t * DB + dl];
+            const float uu = st[kT * DB + t * DB + dl];
+            const float du = delta * uu;
+            const float4 Bv = *reinterpret_cast<const float4*>(Bs + t * NPAD);
+            const float4 Cv = *reinterpret_cast<const float4*>(Cs + t * NPAD);
+            const float bq[kNPT] = {Bv.x, Bv.y, Bv.z, Bv.w}, cq[kNPT] = {Cv.x, Cv.y, Cv.z, Cv.w};
+            float yp = 0.f;
+#pragma unroll
+            for (int q = 0; q < kNPT; ++q) {
+                const float lam = ex2_fast(delta * A2[q]);
+                h[q] = fmaf(lam, h[q], du * bq[q]);
+                yp = fmaf(h[q], cq[q], yp);
+            }
+#pragma unroll
+            for (int off = 1; off < TPC; off <<= 1) yp += __shfl_xor_sync(0xffffffffu, yp, off);
+            if (ng == 0) ob[t * DB + dl] = (yp + Dp * uu) * st[2 * kT * DB + t * DB + dl];
+        }
+        if constexpr (STORE_CHK) {
+            if (tlive == kT && d_ok) {
+                float* ck = p.chk + ((b * p.NC + c) * D + d) * N + n0;
+                if (VEC == 4 && n0 + kNPT <= N) {
+                    *reinterpret_cast<float4*>(ck) = make_float4(h[0], h[1], h[2], h[3]);
+                } else {
+#pragma unroll
+                    for (int q = 0; q < kNPT; ++q)
+                        if (n0 + q < N) ck[q] = h[q];
+                }
+            }
+        }
+    }
+    __syncthreads();
+    if (p.NC > 0) store_out(p.NC - 1);
+    mcp_wait<0>();
+    if (d_ok) {
+#pragma unroll
+        for (int q = 0; q < kNPT; ++q)
+            if (n0 + q < N) p.hlast[(b * D + d) * N + n0 + q] = h[q];
+    }
+}
+
+// ================================================================================ adjoint
+// One butterfly step of the channel reduction: lanes `OFF` apart exchange half of their CNT
+// values and add, so the number of live values per lane halves (or, once a single value is
+// left, plain exchange-and-add).  Upper lanes keep the upper half of the value indices.
+template <int OFF, int CNT>
+__device__ __forceinline__ void rs_step(float (&v)[8], int lane) {
+    if constexpr (CNT > 1) {
+        constexpr int H = CNT / 2;
+        const bool upper = (lane & OFF) != 0;
+#pragma unroll
+        for (int i = 0; i < H; ++i) {
+            const float send = upper ? v[i] : v[i + H];
+            const float keep = upper ? v[i + H] : v[i];
+            v[i] = keep + __shfl_xor_sync(0xffffffffu, send, OFF);
+        }
+    } else {
+        v[0] += __shfl_xor_sync(0xffffffffu, v[0], OFF);
+    }
+}
+
+template <int TPC, int DB, int VEC, int S>
+__global__ void __launch_bounds__(DB* TPC) mamba_bwd_kernel(const MambaArgs p) {
+    constexpr int NTHR = DB * TPC;
+    constexpr int NW = NTHR / 32;
+    constexpr int NPAD = kNPT * TPC;
+    constexpr int TD = kT * DB;
+    constexpr int STAGE = 4 * TD + 2 * kT * NPAD + 4 * NTHR;  // draw,u,z,gout | Bt,Ct | checkpoint
+    extern __shared__ __align__(16) float smem[];
+    float* ring = smem;                          // [S][STAGE]
+    float* sigd = ring + S * STAGE;              // [kT][DB]   sigmoid(draw)
+    float* obuf = sigd + TD;                     // [3][kT][DB] staged gdraw, gu, gz
+    float* red = obuf + 3 * TD;                  // [NW][kT][2][NPAD] per-warp grad_B / grad_C rows
+    float4* hbuf = reinterpret_cast<float4*>(red + NW * kT * 2 * NPAD);  // [kT][NTHR] states
+    float4* lbuf = hbuf + kT * NTHR;                                      // [kT][NTHR] decays
+
+    const int tid = threadIdx.x;
+    const int lane = tid & 31, wid = tid >> 5;
+    const int dl = tid / TPC, ng = tid % TPC;
+    const long long b = blockIdx.x / p.ndb;
+    const long long dblk = blockIdx.x - b * p.ndb;
+    const long long d0 = dblk * DB;
+    const long long d = d0 + dl;
+    const int n0 = ng * kNPT;
+    const long long L = p.L, D = p.D, N = p.N;
+    const bool d_ok = d < D;
+    const int dcols = (int)((D - d0) < DB ? (D - d0) : DB);
+
+    for (int e = tid; e < S * STAGE + 4 * TD + NW * kT * 2 * NPAD; e += NTHR) smem[e] = 0.f;
+    __syncthreads();
+
+    // tiles are visited from the last to the first: visit index i <-> tile c = NC-1-i
+    auto issue = [&](long long c, int slot) {
+        const long long t0 = c * kT;
+        const int rows = (int)((L - t0) < kT ? (L - t0) : kT);
+        float* st = ring + slot * STAGE;
+        const long long off = (b * L + t0) * D + d0;
+        copy_tile<VEC, NTHR>(st, DB, p.draw + off, D, rows, DB, dcols, tid);
+        copy_tile<VEC, NTHR>(st + TD, DB, p.u + off, D, rows, DB, dcols, tid);
+        copy_tile<VEC, NTHR>(st + 2 * TD, DB, p.z + off, D, rows, DB, dcols, tid);
+        copy_tile<VEC, NTHR>(st + 3 * TD, DB, p.gout + off, D, rows, DB, dcols, tid);
+        const long long offn = (b * L + t0) * N;
+        copy_tile<VEC, NTHR>(st + 4 * TD, NPAD, p.Bt + offn, N, rows, NPAD, (int)N, tid);
+        copy_tile<VEC, NTHR>(st + 4 * TD + kT * NPAD, NPAD, p.Ct + offn, N, rows, NPAD, (int)N, tid);
+        // this thread's start state of the tile: checkpoint slot c-1, or h0 for the first tile
+        float* ck = st + 4 * TD + 2 * kT * NPAD + 4 * tid;
+        const float* src = c > 0 ? p.chk + ((b * p.NC + c - 1) * D + d) * N + n0
+                                 : (p.h0 != nullptr ? p.h0 + (b * D + d) * N + n0 : nullptr);
+        if (d_ok && src != nullptr) {
+            if (VEC == 4 && n0 + kNPT <= N) {
+                mcp16(ck, src);
+            } else {
+#pragma unroll
+                for (int q = 0; q < kNPT; ++q)
+                    if (n0 + q < N) mcp4(ck + q, src + q);
+            }
+        }
+    };
+
+#pragma unroll
+    for (int q = 0; q < S - 1; ++q) {
+        if (q < p.NC) issue(p.NC - 1 - q, q);
+        mcp_commit();
+    }
+
+    float A1[kNPT], A2[kNPT], G[kNPT], gA[kNPT], lam_next[kNPT];
+#pragma unroll
+    for (int q = 0; q < kNPT; ++q) {
+        const bool ok = d_ok && (n0 + q) < N;
+        A1[q] = ok ? p.A[d * N + n0 + q] : 0.f;
+        A2[q] = A1[q] * kLog2e;
+        G[q] = (ok && p.ghlast != nullptr) ? p.ghlast[(b * D + d) * N + n0 + q] : 0.f;
+        gA[q] = 0.f;
+        lam_next[q] = 1.f;  // passes ghlast into G_{L-1} unchanged
+    }
+    const float Dp = d_ok ? p.Dp[d] : 0.f;
+    float gDp = 0.f;
+    const bool first_has_h0 = p.h0 != nullptr;
+
+    for (long long i = 0; i < p.NC; ++i) {
+        const long long c = p.NC - 1 - i;
+        const int slot = (int)(i % S);
+        float* st = ring + slot * STAGE;
+        const int tlive = (int)((L - c * kT) < kT ? (L - c * kT) : kT);
+        mcp_wait<S - 2>();
+        __syncthreads();
+        if (i + S - 1 < p.NC) issue(p.NC - 1 - (i + S - 1), (int)((i + S - 1) % S));
+        mcp_commit();
+
+        // once per (t, d): delta, sigmoid(draw), gy = gout*silu(z), gq = gout*d silu(z)/dz
+        for (int e = tid; e < tlive * DB; e += NTHR) {
+            const float x = st[e];
+            st[e] = softplus_f(x);
+            sigd[e] = sigmoid_f(x);
+            const float zz = st[2 * TD + e], go = st[3 * TD + e];
+            const float sz = sigmoid_f(zz);
+            st[2 * TD + e] = go * zz * sz;
+            st[3 * TD + e] = go * sz * (1.f + zz * (1.f - sz));
+        }
+        __syncthreads();
+
+        const float* Bs = st + 4 * TD + n0;
+        const float* Cs = Bs + kT * NPAD;
+        // recompute the tile's states and decays from its start state
+        float h[kNPT];
+        {
+            const float* ck = st + 4 * TD + 2 * kT * NPAD + 4 * tid;
+            const bool have = d_ok && (c > 0 || first_has_h0);
+#pragma unroll
+            for (int q = 0; q < kNPT; ++q) h[q] = (have && n0 + q < N) ? ck[q] : 0.f;
+        }
+        for (int t = 0; t < tlive; ++t) {
+            const float delta = st[t * DB + dl];
+            const float du = delta * st[TD + t * DB + dl];
+            const float4 Bv = *reinterpret_cast<const float4*>(Bs + t * NPAD);
+            const float bq[kNPT] = {Bv.x, Bv.y, Bv.z, Bv.w};
+            float lam[kNPT];
+#pragma unroll
+            for (int q = 0; q < kNPT; ++q) {
+                lam[q] = ex2_fast(delta * A2[q]);
+                h[q] = fmaf(lam[q], h[q], du * bq[q]);
+            }
+            hbuf[t * NTHR + tid] = make_float4(h[0], h[1], h[2], h[3]);
+            lbuf[t * NTHR + tid] = make_float4(lam[0], lam[1], lam[2], lam[3]);
+        }
+
+        // reverse sweep
+        for (int t = tlive - 1; t >= 0; --t) {
+            const float delta = st[t * DB + dl];
+            const float uu = st[TD + t * DB + dl];
+            const float gy = st[2 * TD + t * DB + dl];
+            const float du = delta * uu;
+            const float4 Bv = *reinterpret_cast<const float4*>(Bs + t * NPAD);
+            const float4 Cv = *reinterpret_cast<const float4*>(Cs + t * NPAD);
+            const float4 hv4 = hbuf[t * NTHR + tid];
+            const float bq[kNPT] = {Bv.x, Bv.y, Bv.z, Bv.w}, cq[kNPT] = {Cv.x, Cv.y, Cv.z, Cv.w};
+            const float hv[kNPT] = {hv4.x, hv4.y, hv4.z, hv4.w};
+            float yp = 0.f, gdp = 0.f, gus = 0.f;
+            float vals[8];
+#pragma unroll
+            for (int q = 0; q < kNPT; ++q) {
+                yp = fmaf(hv[q], cq[q], yp);
+                G[q] = fmaf(lam_next[q], G[q], gy * cq[q]);
+                const float lhp = hv[q] - du * bq[q];  // lam_t h_{t-1}
+                vals[q] = G[q] * du;                   // grad_B contribution
+                vals[4 + q] = gy * hv[q];              // grad_C contribution
+                gA[q] = fmaf(G[q] * lhp, delta, gA[q]);
+                gdp = fmaf(G[q], fmaf(A1[q], lhp, uu * bq[q]), gdp);
+                gus = fmaf(G[q], bq[q], gus);
+            }
+#pragma unroll
+            for (int off = 1; off < TPC; off <<= 1) {
+                yp += __shfl_xor_sync(0xffffffffu, yp, off);
+                gdp += __shfl_xor_sync(0xffffffffu, gdp, off);
+                gus += __shfl_xor_sync(0xffffffffu, gus, off);
+            }
+            if (ng == 0) {
+                const float y = yp + Dp * uu;
+                obuf[t * DB + dl] = gdp * sigd[t * DB + dl];
+                obuf[TD + t * DB + dl] = fmaf(delta, gus, gy * Dp);
+                obuf[2 * TD + t * DB + dl] = st[3 * TD + t * DB + dl] * y;
+                gDp = fmaf(gy, uu, gDp);
+            }
+            // sum the 8 values over the channels of this warp; lanes end up owning distinct rows
+            if constexpr (TPC <= 16) rs_step<16, 8>(vals, lane);
+            if constexpr (TPC <= 8) rs_step<8, 4>(vals, lane);
+            if constexpr (TPC <= 4) rs_step<4, 2>(vals, lane);
+            if constexpr (TPC <= 2) rs_step<2, 1>(vals, lane);
+            if constexpr (TPC <= 1) rs_step<1, 1>(vals, lane);
+            {
+                constexpr int CNT = TPC >= 32 ? 8 : (TPC == 16 ? 4 : (TPC == 8 ? 2 : 1));
+                int base = 0;
+                if (TPC <= 16) base += (lane & 16) ? 4 : 0;
+                if (TPC <= 8) base += (lane & 8) ? 2 : 0;
+                if (TPC <= 4) base += (lane & 4) ? 1 : 0;
+                const bool writer = TPC > 2 || (TPC == 2 ? (lane & 2) == 0 : (lane & 3) == 0);
+                if (writer) {
+                    float* r = red + (wid * kT + t) * 2 * NPAD;
+#pragma unroll
+                    for (int k = 0; k < CNT; ++k) {
+                        const int idx = base + k;
+                        r[(idx >> 2) * NPAD + n0 + (idx & 3)] = vals[k];
+                    }
+                }
+            }
+            const float4 l4 = lbuf[t * NTHR + tid];
+            lam_next[0] = l4.x, lam_next[1] = l4.y, lam_next[2] = l4.z, lam_next[3] = l4.w;
+        }
+        __syncthreads();
+
+        // staged per-(t,d) gradients -> global; per-warp grad_B/grad_C rows -> this block's partial
+        {
+            const long long t0 = c * kT;
+            constexpr int PPR = DB / VEC;
+            float* dsts[3] = {p.gdraw, p.gu, p.gz};
+#pragma unroll
+            for (int k = 0; k < 3; ++k) {
+                float* dst = dsts[k] + (b * L + t0) * D + d0;
+                const float* ob = obuf + k * TD;
+                for (int e = tid; e < tlive * PPR; e += NTHR) {
+                    const int r = e / PPR, cc = (e - r * PPR) * VEC;
+                    if (cc < dcols) {
+                        if constexpr (VEC == 4) {
+                            __stcs(reinterpret_cast<float4*>(dst + r * D + cc),
+                                   *reinterpret_cast<const float4*>(ob + r * DB + cc));
+                        } else {
+                            __stcs(dst + r * D + cc, ob[r * DB + cc]);
+                        }
+                    }
+                }
+            }
+            for (int e = tid; e < tlive * 2 * NPAD; e += NTHR) {
+                const int t = e / (2 * NPAD), rem = e - t * 2 * NPAD;
+                const int which = rem / NPAD, n = rem - which * NPAD;
+                if (n < N) {
+                    float s = 0.f;
+#pragma unroll
+                    for (int ww = 0; ww < NW; ++ww) s += red[(ww * kT + t) * 2 * NPAD + rem];
+                    float* dst = which == 0 ? p.gB_part : p.gC_part;
+                    dst[((dblk * p.B + b) * L + t0 + t) * N + n] = s;
+                }
+            }
+        }
+        // the next iteration's first barrier orders these reads before obuf/red are rewritten
+    }
+    mcp_wait<0>();
+
+    if (d_ok) {
+#pragma unroll
+        for (int q = 0; q < kNPT; ++q) {
+            if (n0 + q < N) {
+                p.gA_part[(b * D + d) * N + n0 + q] = gA[q];
+                if (p.gh0 != nullptr) p.gh0[(b * D + d) * N + n0 + q] = lam_next[q] * G[q];
+            }
+        }
+        if (ng == 0) p.gDp_part[b * D + d] = gDp;
+    }
+}
+
+// out[i] = sum_k in[k * stride + i], k ascending (fixed order)
+__global__ void sum_leading_kernel(const float* __restrict__ in, float* __restrict__ out, long long count,
+                                   long long stride, int K) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= count) return;
+    float s = 0.f;
+    for (int k = 0; k < K; ++k) s += in[k * stride + i];
+    out[i] = s;
+}
+
+// ------------------------------------------------------------------------------- host side
+#ifndef MAMBA_FWD_S
+#define MAMBA_FWD_S 4  // ring stages of the forward
+#endif
+#ifndef MAMBA_BWD_S
+#define MAMBA_BWD_S 2  // ring stages of the adjoint (its state buffers take most of shared memory)
+#endif
+constexpr int kMambaThreads = 128;
+
+static int tpc_for(long long N) {  // threads per channel: 4 states each, power of two
+    int t = 1;
+    while ((long long)t * kNPT < N) t *= 2;
+    return t;
+}
+
+template <typename K>
+static int set_smem(K kern, size_t bytes, bool* configured) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes) != cudaSuccess)
+            return B200_ERR_LAUNCH;
+        configured[dev] = true;
+    }
+    return B200_OK;
+}
+
+template <int TPC, bool STORE_CHK, int VEC>
+static int launch_mamba_fwd(const MambaArgs& a, cudaStream_t st) {
+    constexpr int DB = kMambaThreads / TPC, S = MAMBA_FWD_S;
+    constexpr size_t smem = sizeof(float) * ((size_t)S * (3 * kT * DB + 2 * kT * kNPT * TPC) + 2 * kT * DB);
+    auto kern = mamba_fwd_kernel<TPC, DB, STORE_CHK, VEC, S>;
+    static bool configured[64] = {false};
+    if (set_smem(kern, smem, configured) != B200_OK) return B200_ERR_LAUNCH;
+    MambaArgs p = a;
+    p.ndb = (a.D + DB - 1) / DB;
+    const long long grid = a.B * p.ndb;
+    if (grid > 0x7fffffffLL) return B200_ERR_UNSUPPORTED;
+    kern<<<(unsigned int)grid, kMambaThreads, smem, st>>>(p);
+    return cudaGetLastError() == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
+}
+
+template <int TPC, int VEC>
+static int launch_mamba_bwd(const MambaArgs& a, cudaStream_t st) {
+    constexpr int DB = kMambaThreads / TPC, S = MAMBA_BWD_S, NPAD = kNPT * TPC, NW = kMambaThreads / 32;
+    constexpr size_t smem =
+        sizeof(float) * ((size_t)S * (4 * kT * DB + 2 * kT * NPAD + 4 * kMambaThreads) + 4 * kT * DB +
+                         NW * kT * 2 * NPAD + 2 * kT * kMambaThreads * 4);
+    auto kern = mamba_bwd_kernel<TPC, DB, VEC, S>;
+    static bool configured[64] = {false};
+    if (set_smem(kern, smem, configured) != B200_OK) return B200_ERR_LAUNCH;
+    const long long grid = a.B * a.ndb;
+    if (grid > 0x7fffffffLL) return B200_ERR_UNSUPPORTED;
+    kern<<<(unsigned int)grid, kMambaThreads, smem, st>>>(a);
+    return cudaGetLastError() == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
+}
+
+#define B200_TPC_SWITCH(tpc, CALL)    \
+    switch (tpc) {                    \
+        case 1: return CALL(1);       \
+        case 2: return CALL(2);       \
+        case 4: return CALL(4);       \
+        case 8: return CALL(8);       \
+        case 16: return CALL(16);     \
+        case 32: return CALL(32);     \
+        default: return B200_ERR_UNSUPPORTED; \
+    }
+
+static int dispatch_mamba_fwd(int tpc, bool chk, bool vec, const MambaArgs& a, cudaStream_t st) {
+    if (chk && vec) {
+#define CALL(T) launch_mamba_fwd<T, true, 4>(a, st)
+        B200_TPC_SWITCH(tpc, CALL)
+#undef CALL
+    } else if (chk) {
+#define CALL(T) launch_mamba_fwd<T, true, 1>(a, st)
+        B200_TPC_SWITCH(tpc, CALL)
+#undef CALL
+    } else if (vec) {
+#define CALL(T) launch_mamba_fwd<T, false, 4>(a, st)
+        B200_TPC_SWITCH(tpc, CALL)
+#undef CALL
+    } else {
+#define CALL(T) launch_mamba_fwd<T, false, 1>(a, st)
+        B200_TPC_SWITCH(tpc, CALL)
+#undef CALL
+    }
+}
+
+static int dispatch_mamba_bwd(int tpc, bool vec, const MambaArgs& a, cudaStream_t st) {
+    if (vec) {
+#define CALL(T) launch_mamba_bwd<T, 4>(a, st)
+        B200_TPC_SWITCH(tpc, CALL)
+#undef CALL
+    } else {
+#define CALL(T) launch_mamba_bwd<T, 1>(a, st)
+        B200_TPC_SWITCH(tpc, CALL)
+#undef CALL
+    }
+}
+
+struct MambaWs {
+    size_t off_gA, off_gDp, off_gB, off_gC, total;
+    long long ndb;
+};
+
+static MambaWs mamba_ws(long long B, long long L, long long D, long long N) {
+    MambaWs w;
+    const int DB = kMambaThreads / tpc_for(N);
+    w.ndb = (D + DB - 1) / DB;
+    size_t off = 0;
+    w.off_gA = off;
+    off += align_up(sizeof(float) * (size_t)(B * D * N), 256);
+    w.off_gDp = off;
+    off += align_up(sizeof(float) * (size_t)(B * D), 256);
+    w.off_gB = off;
+    off += align_up(sizeof(float) * (size_t)(w.ndb * B * L * N), 256);
+    w.off_gC = off;
+    off += align_up(sizeof(float) * (size_t)(w.ndb * B * L * N), 256);
+    w.total = off;
+    return w;
+}
+
+static int sum_leading(const float* in, float* out, long long count, long long stride, long long K, cudaStream_t st) {
+    if (count == 0) return B200_OK;
+    const long long blocks = (count + 255) / 256;
+    if (blocks > 0x7fffffffLL || K > 0x7fffffffLL) return B200_ERR_UNSUPPORTED;
+    sum_leading_kernel<<<(unsigned int)blocks, 256, 0, st>>>(in, out, count, stride, (int)K);
+    return cudaGetLastError() == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
+}
+
+static bool aligned16(std::initializer_list<const void*> ps) {
+    for (const void* q : ps)
+        if (((uintptr_t)q & 15) != 0) return false;
+    return true;
+}
+
+}  // namespace b200
+
+extern "C" {
+
+int b200_mamba_chk_interval(void) { return b200::kT; }
+
+int b200_mamba_fwd(int64_t B, int64_t L, int64_t D, int64_t N, const void* draw, const void* A, const void* Bt,
+                   const void* Ct, const void* u, const void* z, const void* Dp, const void* h0, void* out,
+                   void* hlast, void* chk, void* stream) {
+    using namespace b200;
+    if (B < 0 || L < 0 || D < 0 || N < 1) return B200_ERR_ARG;
+    if (N > 128) return B200_ERR_UNSUPPORTED;
+    if (B == 0 || D == 0) return B200_OK;
+    if (!A || !Dp || !hlast || (L > 0 && (!draw || !Bt || !Ct || !u || !z || !out))) return B200_ERR_ARG;
+    MambaArgs a = {};
+    a.draw = (const float*)draw, a.A = (const float*)A, a.Bt = (const float*)Bt, a.Ct = (const float*)Ct;
+    a.u = (const float*)u, a.z = (const float*)z, a.Dp = (const float*)Dp, a.h0 = (const float*)h0;
+    a.out = (float*)out, a.chk = (float*)chk, a.hlast = (float*)hlast;
+    a.B = B, a.L = L, a.D = D, a.N = N;
+    a.NC = (L + kT - 1) / kT;
+    const bool vec = D % 4 == 0 && N % 4 == 0 && aligned16({draw, Bt, Ct, u, z, out, chk});
+    return dispatch_mamba_fwd(tpc_for(N), chk != nullptr, vec, a, static_cast<cudaStream_t>(stream));
+}
+
+size_t b200_mamba_bwd_workspace_bytes(int64_t B, int64_t L, int64_t D, int64_t N) {
+    if (B <= 0 || L < 0 || D <= 0 || N < 1 || N > 128) return 256;
+    const size_t t = b200::mamba_ws(B, L, D, N).total;
+    return t ? t : 256;
+}
+
+int b200_mamba_bwd(int64_t B, int64_t L, int64_t D, int64_t N, const void* draw, const void* A, const void* Bt,
+                   const void* Ct, const void* u, const void* z, const void* Dp, const void* h0, const void* chk,
+                   const void* gout, const void* ghlast, void* gdraw, void* gA, void* gBt, void* gCt, void* gu,
+                   void* gz, void* gDp, void* gh0, void* workspace, size_t workspace_bytes, void* stream) {
+    using namespace b200;
+    if (B < 0 || L < 0 || D < 0 || N < 1) return B200_ERR_ARG;
+    if (N > 128) return B200_ERR_UNSUPPORTED;
+    if (B == 0 || D == 0) return B200_OK;
+    if (!A || !Dp || !gA || !gDp || (h0 && !gh0)) return B200_ERR_ARG;
+    if (L > 0 && (!draw || !Bt || !Ct || !u || !z || !gout || !gdraw || !gBt || !gCt || !gu || !gz)) return B200_ERR_ARG;
+    if (L > kT && !chk) return B200_ERR_ARG;
+    const MambaWs w = mamba_ws(B, L, D, N);
+    if (!workspace || ((uintptr_t)workspace % 256) != 0 || workspace_bytes < w.total) return B200_ERR_WORKSPACE;
+    char* base = static_cast<char*>(workspace);
+    MambaArgs a = {};
+    a.draw = (const float*)draw, a.A = (const float*)A, a.Bt = (const float*)Bt, a.Ct = (const float*)Ct;
+    a.u = (const float*)u, a.z = (const float*)z, a.Dp = (const float*)Dp, a.h0 = (const float*)h0;
+    a.chk = (float*)chk;
+    a.gout = (const float*)gout, a.ghlast = (const float*)ghlast;
+    a.gdraw = (float*)gdraw, a.gu = (float*)gu, a.gz = (float*)gz, a.gh0 = h0 ? (float*)gh0 : nullptr;
+    a.gA_part = (float*)(base + w.off_gA), a.gDp_part = (float*)(base + w.off_gDp);
+    a.gB_part = (float*)(base + w.off_gB), a.gC_part = (float*)(base + w.off_gC);
+    a.B = B, a.L = L, a.D = D, a.N = N;
+    a.ndb = w.ndb;
+    a.NC = (L + kT - 1) / kT;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const bool vec = D % 4 == 0 && N % 4 == 0 && aligned16({draw, Bt, Ct, u, z, gout, chk, h0, gdraw, gu, gz});
+    int rc = dispatch_mamba_bwd(tpc_for(N), vec, a, st);
+    if (rc != B200_OK) return rc;
+    // fixed-order reductions of the partial buffers
+    if ((rc = sum_leading(a.gA_part, (float*)gA, D * N, D * N, B, st)) != B200_OK) return rc;
+    if ((rc = sum_leading(a.gDp_part, (float*)gDp, D, D, B, st)) != B200_OK) return rc;
+    if ((rc = sum_leading(a.gB_part, (float*)gBt, B * L * N, B * L * N, w.ndb, st)) != B200_OK) return rc;
+    return sum_leading(a.gC_part, (float*)gCt, B * L * N, B * L * N, w.ndb, st);
+}
+
+}  // extern "C"
