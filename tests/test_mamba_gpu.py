@@ -15,6 +15,13 @@ REL = 1e-4
 GRADS = ("gdraw", "gA", "gBt", "gCt", "gu", "gz", "gDp", "gh0")
 
 
+def _err(a, b):
+    """rel_err with a floor on the reference scale: a gradient that is exactly zero in float64
+    (e.g. grad_A for L=1 from a zero state) comes out as float32 rounding residue (~1e-9)."""
+    a, b = np.asarray(a), np.asarray(b)
+    return float(np.abs(a - b).max() / max(np.abs(b).max(), 1e-4)) if a.size else 0.0
+
+
 def _dev(x):
     return None if x is None else torch.from_numpy(np.array(x, copy=True)).cuda()
 
@@ -44,7 +51,7 @@ def test_golden():
         for k in GRADS:
             ref = getattr(c, f"ref64_{k}")
             if ref is not None:
-                assert rel_err(r[k], ref) < REL, (c.name, k)
+                assert _err(r[k], ref) < REL, (c.name, k)
 
 
 def _case(rng, B, L, D, N, with_h0, with_glast, s4d=False):
@@ -73,7 +80,7 @@ def test_matches_oracle(oracle, B, L, D, N, with_h0, with_glast):
     assert rel_err(out, ro) < REL and rel_err(hlast, rh) < REL
     for k in GRADS:
         if rr[k] is not None:
-            assert rel_err(r[k], rr[k]) < REL, k
+            assert _err(r[k], rr[k]) < REL, k
 
 
 def test_bitwise_repeat():

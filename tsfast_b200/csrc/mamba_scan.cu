@@ -185,7 +185,7 @@ __global__ void __launch_bounds__(DB* TPC) mamba_fwd_kernel(const MambaArgs p) {
 #pragma unroll
             for (int q = 0; q < kNPT; ++q) {
                 const float lam = ex2_fast(delta * A2[q]);
-                h[q] = fmaf(lam, h[q], du * bq[q]);
+                h[q] = fmaf(lam, h[q], __fmul_rn(du, bq[q]));
                 yp = fmaf(h[q], cq[q], yp);
             }
 #pragma unroll
@@ -354,7 +354,7 @@ __global__ void __launch_bounds__(DB* TPC) mamba_bwd_kernel(const MambaArgs p) {
 #pragma unroll
             for (int q = 0; q < kNPT; ++q) {
                 lam[q] = ex2_fast(delta * A2[q]);
-                h[q] = fmaf(lam[q], h[q], du * bq[q]);
+                h[q] = fmaf(lam[q], h[q], __fmul_rn(du, bq[q]));
             }
             hbuf[t * NTHR + tid] = make_float4(h[0], h[1], h[2], h[3]);
             lbuf[t * NTHR + tid] = make_float4(lam[0], lam[1], lam[2], lam[3]);
@@ -377,7 +377,8 @@ __global__ void __launch_bounds__(DB* TPC) mamba_bwd_kernel(const MambaArgs p) {
             for (int q = 0; q < kNPT; ++q) {
                 yp = fmaf(hv[q], cq[q], yp);
                 G[q] = fmaf(lam_next[q], G[q], gy * cq[q]);
-                const float lhp = hv[q] - du * bq[q];  // lam_t h_{t-1}
+                // lam_t h_{t-1} = h_t - v_t, with v_t rounded exactly as in the recurrence (so 0 stays 0)
+                const float lhp = __fsub_rn(hv[q], __fmul_rn(du, bq[q]));
                 vals[q] = G[q] * du;                   // grad_B contribution
                 vals[4 + q] = gy * hv[q];              // grad_C contribution
                 gA[q] = fmaf(G[q] * lhp, delta, gA[q]);
