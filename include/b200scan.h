@@ -54,6 +54,26 @@ int b200_diag_bwd(int dtype, int64_t M, int64_t L, int64_t N, const void* g, con
                   const void* out, const void* x0, void* glam, void* gv, void* gx0,
                   void* workspace, size_t workspace_bytes, void* stream);
 
+/* S1 forward for callers that may not allocate device memory at all.  (No counterpart in the
+ * reference; added for this library's users.)  Think of a controller or observer running an
+ * identified LRU/S5 model inside a fixed-rate loop, or a process that was handed a fixed device
+ * arena by its host application: a cudaMalloc there either is forbidden or costs an unbounded
+ * stall, and even torch's caching allocator may fall through to one.  Same arguments and result
+ * as b200_diag_fwd, minus the workspace: the cross-tile state of the look-back kernel lives in a
+ * 4 MiB array inside the library image (held by every GPU that loads the library until exit).
+ * Limits and rules:
+ *  - problems whose look-back state exceeds 4 MiB are refused with B200_ERR_UNSUPPORTED
+ *    (b200_diag_workspace_bytes(dtype, 0, M, L, N) > 4194304; roughly M * ceil(N/64..128) *
+ *    ceil(L/32) <= 2700 tiles, e.g. 16 x 1000 x 64 complex fits);
+ *  - the first call on each device looks up the array's device address (cudaGetSymbolAddress)
+ *    with that device current; make that first call before any stream capture;
+ *  - every call reuses the one array (it zeroes the words that must start at zero itself), so two
+ *    calls that can overlap on the GPU - different streams, or different host threads - race;
+ *    keep calls of this entry point on one stream or order them with events;
+ *  - it calls no cudaMalloc/cudaFree and no allocating library routine. */
+int b200_diag_fwd_static(int dtype, int64_t M, int64_t L, int64_t N, const void* lam, const void* v,
+                         const void* x0, void* out, void* stream);
+
 /* ---- S2: diagonal scan with time-varying coefficients ---------------------------------
  * x_t = lam_t * x_{t-1} + v_t.   lam, v, out [B,L,N]; x0 [B,N] or NULL.
  * Replaces sel_fwd / sel_bwd of tsfast/models/_core/scan_backends/selective_c.py:52-120 (CPU)

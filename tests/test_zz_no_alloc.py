@@ -1,0 +1,81 @@
+"""The allocation-free S1 forward, b200_diag_fwd_static, against the regular b200_diag_fwd.
+
+Some users of the library cannot allocate device memory where they call it: a fixed-rate control or
+estimation loop, or a process confined to a device arena its host application handed it.  For them
+the library keeps the look-back kernel's cross-tile state in a 4 MiB array of its own.  This test
+calls the entry point through the C ABI twice in a row (the second call meets the first call's
+leftovers in the shared array) and checks both results against the workspace-taking entry point,
+which the parity tests pin to the oracle; it also checks that an oversized problem is refused.
+The file sorts last so that a run stopping at the first failure has already run everything else.
+"""
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def _regular(L_, tag, lam, v, x0):
+    from tsfast_b200 import _lib
+
+    M, L, N = v.shape
+    out = torch.empty_like(v)
+    ws = _lib.workspace(L_.b200_diag_workspace_bytes(tag, 0, M, L, N), v.device)
+    _lib.check(L_.b200_diag_fwd(tag, M, L, N, _ptr(lam), _ptr(v), _ptr(x0), _ptr(out), _ptr(ws), ws.numel(),
+                                _lib.stream_ptr(v.device)), "b200_diag_fwd")
+    return out
+
+
+def _static(L_, tag, lam, v, x0):
+    from tsfast_b200 import _lib
+
+    M, L, N = v.shape
+    out = torch.empty_like(v)
+    _lib.check(L_.b200_diag_fwd_static(tag, M, L, N, _ptr(lam), _ptr(v), _ptr(x0), _ptr(out),
+                                       _lib.stream_ptr(v.device)), "b200_diag_fwd_static")
+    return out
+
+
+@pytest.mark.parametrize("cplx", [True, False])
+def test_static_scratch_matches_regular_entry_point_twice(cplx):
+    from tsfast_b200 import _lib
+
+    L_ = _lib.lib()
+    torch.manual_seed(3)
+    dt = torch.complex64 if cplx else torch.float32
+    tag = _lib.dtype_tag(dt)
+    cases = [(16, 1000, 64), (3, 257, 24)]  # several time tiles per chain, so the look-back state is used
+    for M, L, N in cases:
+        mag = torch.rand(M, N, device="cuda") * 0.1 + 0.89
+        lam = (mag * torch.exp(1j * torch.rand(M, N, device="cuda") * 0.3)).to(dt) if cplx else mag
+        for trial in range(2):  # two calls in a row share the scratch array
+            v = torch.randn(M, L, N, device="cuda", dtype=dt)
+            x0 = torch.randn(M, N, device="cuda", dtype=dt) if trial == 0 else None
+            want = _regular(L_, tag, lam, v, x0)
+            got = _static(L_, tag, lam, v, x0)
+            torch.cuda.synchronize()
+            scale = want.abs().max().item()
+            # same tolerance as the parity tests: max|a-b| / max|b| < 1e-4
+            assert (got - want).abs().max().item() < 1e-4 * scale, (M, L, N, trial)
+
+
+def test_static_scratch_refuses_oversized_problem():
+    from tsfast_b200 import _lib
+
+    L_ = _lib.lib()
+    M, L, N = 64, 4096, 256
+    assert L_.b200_diag_workspace_bytes(0, 0, M, L, N) > (4 << 20)
+    lam = torch.rand(M, N, device="cuda")
+    v = torch.zeros(M, L, N, device="cuda")
+    out = torch.full_like(v, 7.0)
+    rc = L_.b200_diag_fwd_static(0, M, L, N, _ptr(lam), _ptr(v), None, _ptr(out), _lib.stream_ptr(v.device))
+    assert rc == 4  # B200_ERR_UNSUPPORTED
+    torch.cuda.synchronize()
+    assert float(out.min()) == 7.0  # nothing was launched
+    with pytest.raises(RuntimeError, match="UNSUPPORTED"):
+        _lib.check(rc, "b200_diag_fwd_static")

@@ -33,6 +33,7 @@ SIGNATURES = {
     "b200_diag_workspace_bytes": (_sz, [_int, _int, _i64, _i64, _i64]),
     "b200_diag_fwd": (_int, [_int, _i64, _i64, _i64] + [_vp] * 5 + [_sz, _vp]),
     "b200_diag_bwd": (_int, [_int, _i64, _i64, _i64] + [_vp] * 8 + [_sz, _vp]),
+    "b200_diag_fwd_static": (_int, [_int, _i64, _i64, _i64] + [_vp] * 5),
     "b200_sel_workspace_bytes": (_sz, [_int, _int, _i64, _i64, _i64]),
     "b200_sel_fwd": (_int, [_int, _i64, _i64, _i64] + [_vp] * 5 + [_sz, _vp]),
     "b200_sel_bwd": (_int, [_int, _i64, _i64, _i64] + [_vp] * 8 + [_sz, _vp]),

@@ -944,7 +944,7 @@ static int dispatch(int dtype, const DiagArgs& a, const DiagPlan& pl, cudaStream
 
 static int run(int dtype, bool vary, bool bwd, long long M, long long L, long long N, const void* coef,
                const void* val, const void* xsrc, const void* x0, void* out, void* gcoef, void* gx0,
-               void* ws, size_t ws_bytes, void* stream) {
+               void* ws, size_t ws_bytes, void* stream, bool tiles_only = false) {
     if (dtype != B200_F32 && dtype != B200_C64) return B200_ERR_ARG;
     if (M < 0 || L < 0 || N < 0) return B200_ERR_ARG;
     if (M == 0 || L == 0 || N == 0) return B200_OK;
@@ -973,8 +973,10 @@ static int run(int dtype, bool vary, bool bwd, long long M, long long L, long lo
     a.N = N;
     a.hdr = reinterpret_cast<WsHeader*>(base);
 
-    int mode = 0;  // 0 auto, 1 look-back tiles, 2 streaming chains (tuning aid)
-    if (const char* f = getenv("B200SCAN_DIAG_MODE")) mode = atoi(f);
+    int mode = tiles_only ? 1 : 0;  // 0 auto, 1 look-back tiles, 2 streaming chains (tuning aid)
+    if (!tiles_only) {
+        if (const char* f = getenv("B200SCAN_DIAG_MODE")) mode = atoi(f);
+    }
     const int sv = mode == 1 ? 0 : stream_v(dtype, M, N, por);
     if (sv > 0 || mode == 2) {
         const int V = sv > 0 ? sv : choose_v(dtype, N, por);
@@ -1003,9 +1005,50 @@ static int run(int dtype, bool vary, bool bwd, long long M, long long L, long lo
     return bwd ? dispatch<false, true>(dtype, a, pl, st) : dispatch<false, false>(dtype, a, pl, st);
 }
 
+// ---------------------------------------------------------------- scratch for b200_diag_fwd_static
+// Cross-tile state (tickets, flags, aggregates) of the look-back kernel for callers that cannot
+// hand in a workspace.  It lives in the library image: every GPU that loads the library holds
+// these 4 MiB until the process exits.  In host code `g_static_scratch` is only a handle for
+// cudaGetSymbolAddress; the kernels get the device address that call returns.
+constexpr size_t kStaticScratchBytes = size_t(4) << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// Device address of the scratch array on the current device (looked up once per device).
+static void* static_scratch_addr(int* rc) {
+    static void* addr[64] = {nullptr};
+    int dev = 0;
+    *rc = B200_OK;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+        *rc = B200_ERR_LAUNCH;
+        return nullptr;
+    }
+    if (addr[dev] == nullptr) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || p == nullptr) {
+            *rc = B200_ERR_LAUNCH;
+            return nullptr;
+        }
+        addr[dev] = p;
+    }
+    return addr[dev];
+}
+
 }  // namespace b200
 
 extern "C" {
+
+int b200_diag_fwd_static(int dtype, int64_t M, int64_t L, int64_t N, const void* lam, const void* v,
+                         const void* x0, void* out, void* stream) {
+    if (dtype != B200_F32 && dtype != B200_C64) return B200_ERR_ARG;
+    if (M < 0 || L < 0 || N < 0) return B200_ERR_ARG;
+    if (M == 0 || L == 0 || N == 0) return B200_OK;
+    if (b200::workspace_bytes(dtype, false, false, M, L, N) > b200::kStaticScratchBytes) return B200_ERR_UNSUPPORTED;
+    int rc = B200_OK;
+    void* scratch = b200::static_scratch_addr(&rc);
+    if (rc != B200_OK) return rc;
+    return b200::run(dtype, false, false, M, L, N, lam, v, nullptr, x0, out, nullptr, nullptr, scratch,
+                     b200::kStaticScratchBytes, stream, /*tiles_only=*/true);
+}
 
 size_t b200_diag_workspace_bytes(int dtype, int backward, int64_t M, int64_t L, int64_t N) {
     if (M <= 0 || L <= 0 || N <= 0) return 256;
