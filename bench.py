@@ -34,6 +34,7 @@ TENSOR_BYTES = B * T * D * 4
 FWD_BYTES = 3 * TENSOR_BYTES  # a, b -> h
 BWD_BYTES = 5 * TENSOR_BYTES  # g, a, h -> ga, gb
 STEP_BYTES = FWD_BYTES + BWD_BYTES
+ADJOINT_DRAM_TRAFFIC_BYTES = 805_204_224 + 495_119_360
 METRIC = "scan GB/s (fwd+bwd)"
 WORKLOAD = "C2: time-varying diagonal scan fwd+bwd, B=64 T=4096 D=256 fp32 per GPU, h0=0"
 
@@ -205,7 +206,7 @@ def run_gpu(args):
     torch.cuda.synchronize()
     s0.record()
     for _ in range(n):
-        sel.forward(a, b, None)
+        h = sel.forward(a, b, None)
     s1.record()
     for _ in range(n):
         sel.backward(g, a, h, None)
@@ -285,9 +286,9 @@ def _report(args, world, rank, ms, e2e_ms, fwd_ms, bwd_ms, clock_rec):
             "gpu_launches": 2 * args.steps,
             "clocks": clock_rec,
         }
-        traffic = ROOT / "profiles" / "traffic.json"
-        if traffic.exists():  # DRAM bytes per adjoint launch from the committed ncu capture
-            line["roofline"]["traffic"] = json.loads(traffic.read_text()).get("sel_bwd_c2_bytes")
+        # dram__bytes_read.sum + dram__bytes_write.sum of one adjoint launch at this workload, from the
+        # ncu capture summarised in profiles/sel_scan_c2_ncu_full.md
+        line["roofline"]["traffic"] = ADJOINT_DRAM_TRAFFIC_BYTES
         print(json.dumps(line))
 
 
