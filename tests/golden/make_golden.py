@@ -253,9 +253,35 @@ def make_allpole():
     print("allpole", len(names), "cases")
 
 
+# ------------------------------------------------------------------ DeepLRU caller stack
+def make_lru():
+    """A small reference DeepLRU (tsfast/models/architectures/lru.py) in float64: parameters,
+    input, output, carried states, and the gradient of sum(y * g) w.r.t. every parameter."""
+    from tsfast.models.architectures.lru import DeepLRU
+
+    torch.manual_seed(42)
+    model = DeepLRU(2, 3, d_model=8, d_state=6, n_layers=2, r_min=0.5, r_max=0.98, max_phase=1.0,
+                    return_state=True).double()
+    with use_backend("reference"):
+        gen = torch.Generator().manual_seed(4000)
+        u = torch.randn(3, 40, 2, generator=gen, dtype=torch.float64)
+        g = torch.randn(3, 40, 3, generator=gen, dtype=torch.float64)
+        y, states = model(u)
+        (y * g).sum().backward()
+    store = {"u": _np(u), "g": _np(g), "y": _np(y)}
+    for i, s in enumerate(states):
+        store[f"state{i}"] = _np(s)
+    for k, v in model.state_dict().items():
+        store[f"param/{k}"] = _np(v)
+    for k, v in model.named_parameters():
+        store[f"grad/{k}"] = _np(v.grad)
+    np.savez_compressed(HERE / "deeplru.npz", **store)
+    print("deeplru", len(store), "arrays")
+
+
 if __name__ == "__main__":
     torch.set_num_threads(4)
-    which = sys.argv[1:] or ["diag", "sel", "mamba", "allpole"]
+    which = sys.argv[1:] or ["diag", "sel", "mamba", "allpole", "lru"]
     if "diag" in which:
         make_diag("diag")
     if "sel" in which:
@@ -264,3 +290,5 @@ if __name__ == "__main__":
         make_mamba()
     if "allpole" in which:
         make_allpole()
+    if "lru" in which:
+        make_lru()
