@@ -6,13 +6,15 @@ h0 = 0, upstream gradient ~ N(0,1), all synthetic and seeded.  One step = one fo
 of compulsory HBM traffic, the figure every GB/s number below is computed from.  With N GPUs every
 rank scans its own 64 sequences (weak scaling; the scan has no collective).
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload C1..C5]
 
 Prints ONE JSON line: `value` is device-resident throughput (inputs already in HBM), `e2e` the
 same metric through the public API from pinned HOST buffers with the host<->device copies inside
 the timed region, `roofline` the dominant kernel (the adjoint) against the measured HBM peak, and
 `cpu_baseline` the CPU oracle (a C port of the reference's CPU kernels) on the host cores.
 `--impl reference` times that CPU port alone and prints the same line shape.
+`--workload C1|C3|C4|C5` measures the other configurations the same way (complex LRU scan, Mamba
+section, all-pole filter, DeepLRU data-parallel training step); C2 is the headline.
 """
 
 from __future__ import annotations
@@ -292,12 +294,361 @@ def _report(args, world, rank, ms, e2e_ms, fwd_ms, bwd_ms, clock_rec):
         print(json.dumps(line))
 
 
+# ----------------------------------------------------------------------------- other workloads
+# C1, C3, C4 (one scan each) and C5 (DeepLRU training step).  Same JSON line as the default
+# workload; per-step events, with an L2 flush between steps where the working set fits in L2.
+def _workload(name, torch, dev, rank):
+    """Returns dict(desc, fwd_bytes, bwd_bytes, elems, fwd(), bwd(out), e2e(), cpu(rows)->sec, rows, flush)."""
+    import numpy as np
+
+    import tsfast_b200
+    from tsfast_b200 import allpole_b200, mamba_b200
+    from tsfast_b200.scan_backends import diagonal_b200
+
+    gen = torch.Generator(device=dev).manual_seed(1234 + rank)
+    rn = lambda *s: torch.randn(*s, device=dev, generator=gen)  # noqa: E731
+    pin = lambda t: torch.empty(t.shape, dtype=t.dtype, pin_memory=True).copy_(t)  # noqa: E731
+    if name == "C1":
+        M, L, N = 16, 1000, 64
+        r = torch.rand(N, device=dev, generator=gen) * 0.099 + 0.9
+        th = torch.rand(N, device=dev, generator=gen) * (np.pi / 10)
+        lam1 = torch.polar(r, th)
+        lam = lam1.expand(M, N).contiguous()
+        cn = lambda *s: torch.complex(rn(*s), rn(*s)) * (0.5**0.5)  # noqa: E731
+        v, g, x0 = cn(M, L, N), cn(M, L, N), cn(M, N) * (0.1**0.5)
+        E = M * L * N * 8
+        hv, hg, hx0 = pin(v), pin(g), pin(x0)
+        ho, hgv = pin(v), pin(v)
+
+        def e2e():
+            dv, dx0 = hv.to(dev, non_blocking=True).requires_grad_(), hx0.to(dev, non_blocking=True).requires_grad_()
+            l1 = lam1.clone().requires_grad_()
+            out = tsfast_b200.diagonal_recurrence(l1, dv, dx0)
+            out.backward(hg.to(dev, non_blocking=True))
+            ho.copy_(out.detach(), non_blocking=True)
+            hgv.copy_(dv.grad, non_blocking=True)
+            return l1.grad.cpu()
+
+        def cpu(rows):
+            from oracle import oracle as O
+            a_, v_, g_, x_ = (t[:rows].cpu().numpy() for t in (lam, v, g, x0))
+            return lambda: O.diag_bwd(g_, a_, O.diag_fwd(a_, v_, x_), x_)
+
+        return dict(desc="C1: complex LRU diagonal scan fwd+bwd, B=16 T=1000 D=64 complex64, carry-in x0",
+                    fwd_bytes=2 * E, bwd_bytes=3 * E, elems=2 * M * L * N, rows=M, sample_rows=M, flush=True,
+                    h2d=3 * E, d2h=2 * E, dtype="c64", launches=2, kernel="diag_scan_kernel<float2, const, adjoint> (b200_diag_bwd)",
+                    fwd=lambda: diagonal_b200.forward(lam, v, x0), bwd=lambda o: diagonal_b200.backward(g, lam, o, x0),
+                    e2e=e2e, cpu=cpu)
+    if name == "C3":
+        Bn, L, D, N = 32, 2048, 512, 16
+        draw = rn(Bn, L, D) * 0.5 - 3.0
+        A = -torch.arange(1, N + 1, device=dev, dtype=torch.float32).expand(D, N).contiguous()
+        Bt, Ct, u, z, gout = rn(Bn, L, N), rn(Bn, L, N), rn(Bn, L, D), rn(Bn, L, D), rn(Bn, L, D)
+        Dp = torch.ones(D, device=dev)
+        ins = (draw, A, Bt, Ct, u, z, Dp, None)
+        big, small = Bn * L * D * 4, Bn * L * N * 4
+        hin = [pin(t) for t in (draw, Bt, Ct, u, z, gout)]
+        hout = [pin(draw) for _ in range(4)] + [pin(Bt), pin(Bt)]
+
+        def e2e():
+            d_, b_, c_, u_, z_, g_ = (t.to(dev, non_blocking=True) for t in hin)
+            leaves = [t.requires_grad_() for t in (d_, b_, c_, u_, z_)]
+            A_, Dp_ = A.clone().requires_grad_(), Dp.clone().requires_grad_()
+            out, _ = mamba_b200.run(leaves[0], A_, leaves[1], leaves[2], leaves[3], leaves[4], Dp_, None)
+            out.backward(g_)
+            for h_, t in zip(hout, (out.detach(), d_.grad, u_.grad, z_.grad, b_.grad, c_.grad)):
+                h_.copy_(t, non_blocking=True)
+            return A_.grad.cpu()
+
+        def cpu(rows):
+            from oracle import oracle as O
+            a = [t[:rows].cpu().numpy() if t is not None and t.dim() == 3 else (None if t is None else t.cpu().numpy()) for t in ins]
+            go = gout[:rows].cpu().numpy()
+            return lambda: (O.mamba_fwd(*a), O.mamba_bwd(*a, go, None))
+
+        return dict(desc="C3: Mamba selective scan fwd+bwd, B=32 T=2048 D_inner=512 N=16 fp32, S4D-real A, D=1, SiLU gate",
+                    fwd_bytes=4 * big + 2 * small + Bn * D * N * 4, bwd_bytes=7 * big + 4 * small,
+                    elems=2 * Bn * L * D * N, rows=Bn, sample_rows=2, flush=False, h2d=4 * big + 2 * small + big,
+                    d2h=4 * big + 2 * small, dtype="f32", launches=6, kernel="mamba_bwd_kernel<TPC=4> (b200_mamba_bwd)",
+                    fwd=lambda: mamba_b200._scan_train_op(*ins), bwd=lambda o: mamba_b200._scan_bwd_op(gout, None, o[2], *ins),
+                    e2e=e2e, cpu=cpu)
+    if name == "C4":
+        P, Bn, L = 128, 128, 8192
+        rng = np.random.default_rng(1234 + rank)
+        a0 = np.zeros((P, 4))
+        for i in range(P):
+            poles = []
+            for _ in range(2):
+                rr, th = rng.uniform(0.5, 0.95), rng.uniform(0, np.pi)
+                poles += [rr * np.exp(1j * th), rr * np.exp(-1j * th)]
+            a0[i] = np.real(np.poly(poles))[1:]
+        a_p = torch.from_numpy(a0.astype(np.float32)).to(dev)
+        a = a_p.expand(Bn, P, 4).reshape(-1, 4).contiguous()
+        w, g = rn(Bn * P, L), rn(Bn * P, L)
+        E = Bn * P * L * 4
+        hw, hg, hy, hgw = pin(w), pin(g), pin(w), pin(w)
+
+        def e2e():
+            dw = hw.to(dev, non_blocking=True).view(Bn, P, L).requires_grad_()
+            ap = a_p.clone().requires_grad_()
+            y = allpole_b200.run(ap, dw, None)
+            y.backward(hg.to(dev, non_blocking=True).view(Bn, P, L))
+            hy.copy_(y.detach().view(-1, L), non_blocking=True)
+            hgw.copy_(dw.grad.view(-1, L), non_blocking=True)
+            return ap.grad.cpu()
+
+        def cpu(rows):
+            from oracle import oracle as O
+            a_, w_, g_ = a[: rows * P].cpu().numpy(), w[: rows * P].cpu().numpy(), g[: rows * P].cpu().numpy()
+            return lambda: O.allpole_bwd(g_, a_, O.allpole_fwd(a_, w_, None), None)
+
+        return dict(desc="C4: dynoNet all-pole IIR scan fwd+bwd, B=128 x 128 channels, T=8192 fp32, order 4",
+                    fwd_bytes=2 * E, bwd_bytes=3 * E, elems=2 * Bn * P * L, rows=Bn, sample_rows=8, flush=False,
+                    h2d=2 * E, d2h=2 * E, dtype="f32", launches=2, kernel="allpole_kernel<NA=4, adjoint> (b200_allpole_bwd)",
+                    fwd=lambda: allpole_b200._allpole_op(a, w, None), bwd=lambda o: allpole_b200._allpole_bwd_op(g, a, o, None),
+                    e2e=e2e, cpu=cpu)
+    raise SystemExit(f"unknown workload {name}")
+
+
+def run_workload(args):
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device (the product has no CPU path; use --impl reference)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    if args.workload == "C5":
+        return _run_c5(args, torch, dist, dev, world, rank, local)
+    wl = _workload(args.workload, torch, dev, rank)
+    flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if wl["flush"] else None
+
+    def barrier():
+        if world > 1:
+            dist.barrier(device_ids=[local])
+        torch.cuda.synchronize()
+
+    def timed(fn, n):
+        """Sum of per-call device times of fn() over n calls (L2 flushed before each when needed)."""
+        tot = 0.0
+        for _ in range(n):
+            if flush_buf is not None:
+                flush_buf.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            e1.synchronize()
+            tot += e0.elapsed_time(e1)
+        return tot / n
+
+    keep = {}
+
+    def step():
+        keep["o"] = wl["fwd"]()
+        wl["bwd"](keep["o"])
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    clocks = ClockSampler(local)
+    if rank == 0:
+        clocks.start()
+    ms = timed(step, args.steps)
+    barrier()
+    clock_rec = clocks.stop() if rank == 0 else None
+    n = max(3, min(args.steps, 10))
+    fwd_ms = timed(lambda: keep.__setitem__("o", wl["fwd"]()), n)
+    bwd_ms = timed(lambda: wl["bwd"](keep["o"]), n)
+    e2e_ms = float("nan")
+    if not args.kernel_only:
+        wl["e2e"]()
+        barrier()
+        e2e_ms = timed(wl["e2e"], max(2, min(args.steps, 5)))
+    times = torch.tensor([ms, e2e_ms], device=dev)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms, e2e_ms = (float(x) for x in times.tolist())
+    if rank == 0:
+        peak, peak_src = _peaks()
+        step_bytes = wl["fwd_bytes"] + wl["bwd_bytes"]
+        base = None
+        if world == 1 and not args.no_cpu and not args.kernel_only:
+            from oracle import oracle as O
+            O.build()
+            rows = wl["sample_rows"]
+            sec, cnt = _time_cpu(wl["cpu"](rows), 1, 1, 10.0)
+            base = {"value": round(step_bytes * rows / wl["rows"] / sec / 1e9, 3), "unit": "GB/s", "cores": O.num_threads(),
+                    "kind": "port", "sample": f"{rows} of {wl['rows']} batch rows, fwd+bwd, median of {cnt} passes of "
+                    f"{sec * 1e3:.1f} ms; float32 C port of the reference's CPU algorithm, OpenMP"}
+        bwd_gbs, fwd_gbs = wl["bwd_bytes"] / bwd_ms / 1e6, wl["fwd_bytes"] / fwd_ms / 1e6
+        print(json.dumps({
+            "metric": METRIC, "value": round(step_bytes * world / ms / 1e6, 1), "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": wl["dtype"], "data": "synthetic",
+            "config": {"workload": wl["desc"], "algorithmic_bytes_per_step_per_gpu": step_bytes,
+                       "state_elements_per_s": round(wl["elems"] * world / (ms * 1e-3)),
+                       "l2": ("working set fits in L2: a 256 MB buffer is rewritten before every timed call"
+                              if wl["flush"] else "streamed tensors are larger than the 126 MB L2; no flush needed"),
+                       "timing": "CUDA events around every step, summed", "sharding": "independent sequences per rank, no collective"},
+            "roofline": {"bound": "hbm", "kernel": wl["kernel"], "achieved": round(bwd_gbs, 1), "peak": peak, "unit": "GB/s",
+                         "frac": round(bwd_gbs / peak, 4), "traffic": None, "peak_source": peak_src,
+                         "algorithmic_bytes_per_launch": wl["bwd_bytes"], "ms_per_launch": round(bwd_ms, 4),
+                         "forward_kernel": {"achieved": round(fwd_gbs, 1), "frac": round(fwd_gbs / peak, 4),
+                                            "algorithmic_bytes_per_launch": wl["fwd_bytes"], "ms_per_launch": round(fwd_ms, 4)}},
+            "cpu_baseline": base,
+            "e2e": None if args.kernel_only else {"value": round(step_bytes * world / e2e_ms / 1e6, 2), "unit": "GB/s",
+                                                  "h2d_bytes_per_step": wl["h2d"], "d2h_bytes_per_step": wl["d2h"],
+                                                  "ms_per_step": round(e2e_ms, 3)},
+            "gpu_launches": wl["launches"] * args.steps, "clocks": clock_rec}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def _run_c5(args, torch, dist, dev, world, rank, local):
+    """C5: DeepLRU (1 in, 1 out, 4 blocks, width 128, 256 complex states) training step, data parallel.
+
+    Every rank holds 128 windows of T=2000 (1024 windows on 8 GPUs): band-limited Gaussian noise in
+    (sigma 0.1, cut-off 0.4 Nyquist), a seeded stable 2nd-order filter followed by tanh as target.
+    Step = forward, MSE, backward, one flat-bucket NCCL all-reduce of the gradients, Adam update.
+    `value` counts the algorithmic bytes of the eight scan passes (4 blocks x (2 + 3) complex
+    tensors of 524 MB) per step time; the scan kernels are also timed alone at the layer shape.
+    """
+    import numpy as np
+    from scipy import signal
+
+    from tsfast_b200.dist import allreduce_gradients
+    from tsfast_b200.lru_model import DeepLRU
+    from tsfast_b200.scan_backends import diagonal_b200
+
+    Bn, T, dm, ds, nl = 128, 2000, 128, 256, 4
+    rng = np.random.default_rng(100 + rank)
+    bl, al = signal.butter(4, 0.4)
+    x_np = signal.lfilter(bl, al, rng.standard_normal((Bn, T + 200)), axis=1)[:, 200:]
+    x_np = 0.1 * x_np / x_np.std()
+    sys_rng = np.random.default_rng(7)  # the plant is the same on every rank
+    pr, pth = sys_rng.uniform(0.7, 0.95), sys_rng.uniform(0.1, 0.6)
+    den = [1.0, -2 * pr * np.cos(pth), pr * pr]
+    y_np = np.tanh(signal.lfilter([sum(den)], den, x_np, axis=1) * 5.0)
+    hx = torch.from_numpy(x_np.astype(np.float32)).unsqueeze(-1).pin_memory()
+    hy = torch.from_numpy(y_np.astype(np.float32)).unsqueeze(-1).pin_memory()
+    xb, yb = hx.to(dev), hy.to(dev)
+
+    torch.manual_seed(0)  # identical replicas
+    model = DeepLRU(1, 1, d_model=dm, d_state=ds, n_layers=nl, r_min=0.0, r_max=1.0).to(dev)
+    opt = torch.optim.Adam(model.parameters(), lr=1e-3)
+    n_params = sum(p.numel() for p in model.parameters())
+    ar_ms = []
+
+    def step(x, y):
+        opt.zero_grad(set_to_none=True)
+        loss = torch.nn.functional.mse_loss(model(x), y)
+        loss.backward()
+        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a0.record()
+        allreduce_gradients(model.parameters(), average=True)
+        a1.record()
+        opt.step()
+        ar_ms.append((a0, a1))
+        return loss
+
+    def barrier():
+        if world > 1:
+            dist.barrier(device_ids=[local])
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step(xb, yb)
+    barrier()
+    ar_ms.clear()
+    clocks = ClockSampler(local)
+    if rank == 0:
+        clocks.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        loss = step(xb, yb)
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1) / args.steps
+    clock_rec = clocks.stop() if rank == 0 else None
+    allreduce_ms = statistics.mean(a.elapsed_time(b) for a, b in ar_ms)
+
+    # end to end: the batch comes from pinned host memory every step, the loss goes back
+    e2e_steps = max(2, min(args.steps, 5))
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    t0.record()
+    for _ in range(e2e_steps):
+        lval = step(hx.to(dev, non_blocking=True), hy.to(dev, non_blocking=True)).item()
+    t1.record()
+    barrier()
+    e2e_ms = t0.elapsed_time(t1) / e2e_steps
+
+    # the scan kernels alone at the layer shape (complex64, M=128, L=2000, N=256)
+    lam = model.blocks[0].lru.eigenvalues().detach().expand(Bn, ds).contiguous()
+    v = torch.randn(Bn, T, ds, device=dev, dtype=torch.complex64)
+    g = torch.randn(Bn, T, ds, device=dev, dtype=torch.complex64)
+    out = diagonal_b200.forward(lam, v, None)
+    k0, k1, k2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+    torch.cuda.synchronize()
+    k0.record()
+    for _ in range(5):
+        out = diagonal_b200.forward(lam, v, None)
+    k1.record()
+    for _ in range(5):
+        diagonal_b200.backward(g, lam, out, None)
+    k2.record()
+    torch.cuda.synchronize()
+    fwd_ms, bwd_ms = k0.elapsed_time(k1) / 5, k1.elapsed_time(k2) / 5
+
+    times = torch.tensor([ms, e2e_ms], device=dev)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms, e2e_ms = (float(x) for x in times.tolist())
+    if rank == 0:
+        peak, peak_src = _peaks()
+        E = Bn * T * ds * 8
+        scan_bytes = nl * 5 * E
+        bwd_gbs, fwd_gbs = 3 * E / bwd_ms / 1e6, 2 * E / fwd_ms / 1e6
+        print(json.dumps({
+            "metric": METRIC, "value": round(scan_bytes * world / ms / 1e6, 1), "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 3), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "c64", "data": "synthetic",
+            "config": {"workload": "C5: DeepLRU(1,1,d_model=128,d_state=256,n_layers=4) training step, "
+                                   f"{Bn} windows of T={T} per GPU ({Bn * world} global), Adam, NCCL gradient all-reduce",
+                       "algorithmic_scan_bytes_per_step_per_gpu": scan_bytes, "windows_per_s": round(Bn * world / (ms * 1e-3), 1),
+                       "parameters": n_params, "allreduce_ms": round(allreduce_ms, 3),
+                       "scan_share_of_step": round(nl * (fwd_ms + bwd_ms) / ms, 3), "final_loss": round(float(lval), 6),
+                       "l2": "every scan tensor is 524 MB, larger than L2; no flush needed",
+                       "note": "value counts scan bytes only; the step also runs the projections, norms and GLU in PyTorch"},
+            "roofline": {"bound": "hbm", "kernel": "diag_stream_kernel<float2, const, adjoint> (b200_diag_bwd)",
+                         "achieved": round(bwd_gbs, 1), "peak": peak, "unit": "GB/s", "frac": round(bwd_gbs / peak, 4),
+                         "traffic": None, "peak_source": peak_src, "algorithmic_bytes_per_launch": 3 * E,
+                         "ms_per_launch": round(bwd_ms, 4),
+                         "forward_kernel": {"achieved": round(fwd_gbs, 1), "frac": round(fwd_gbs / peak, 4),
+                                            "algorithmic_bytes_per_launch": 2 * E, "ms_per_launch": round(fwd_ms, 4)}},
+            "cpu_baseline": None,
+            "e2e": {"value": round(scan_bytes * world / e2e_ms / 1e6, 2), "unit": "GB/s",
+                    "h2d_bytes_per_step": 2 * Bn * T * 4, "d2h_bytes_per_step": 4, "ms_per_step": round(e2e_ms, 3)},
+            "gpu_launches": 2 * nl * args.steps, "clocks": clock_rec}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
+    ap.add_argument("--workload", choices=["C1", "C2", "C3", "C4", "C5"], default="C2")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
     ap.add_argument("--kernel-only", action="store_true",
                     help="device-resident timing only (no end-to-end or CPU leg): the command profiled under ncu")
@@ -305,8 +656,10 @@ def main():
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         run_reference(args)
-    else:
+    elif args.workload == "C2":
         run_gpu(args)
+    else:
+        run_workload(args)
 
 
 if __name__ == "__main__":
