@@ -95,6 +95,18 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
+def _time_cpu(fn, steps, warmup, seconds_target):
+    """Median wall time of fn() over at least `steps` passes, stopping after about seconds_target."""
+    for _ in range(max(1, warmup)):
+        fn()
+    times, t_end = [], time.perf_counter() + seconds_target
+    while len(times) < max(1, steps) or (time.perf_counter() < t_end and len(times) < 50):
+        t0 = time.perf_counter()
+        fn()
+        times.append(time.perf_counter() - t0)
+    return statistics.median(times), len(times)
+
+
 # ----------------------------------------------------------------------------- CPU arm
 def cpu_sample(seconds_target: float = 12.0, steps: int = 1, warmup: int = 1):
     """Time the CPU oracle (float32, all host threads) on a slice of the workload.
