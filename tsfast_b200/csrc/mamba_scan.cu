@@ -16,9 +16,10 @@
 //
 // Training: the forward also writes the state every kT steps (chk [B, ceil(L/kT), D, N], slot k =
 // state after step (k+1)*kT - 1), 1/16 of a full state store.  The adjoint walks the tiles in
-// reverse: it recomputes the tile's states and decays from the checkpoint into shared memory
-// (one exp per state and step again), then sweeps the tile backwards running
-// G_t = gy_t C_t + lam_{t+1} G_{t+1}.  Reductions over channels (grad_B, grad_C) are done in
+// reverse: it recomputes the tile's 16 states per thread from the checkpoint into registers, then
+// sweeps the tile backwards running G_t = gy_t C_t + lam_{t+1} G_{t+1} (the decays are evaluated
+// again on the way back: two exps per state and step, which buys the registers/shared memory for
+// three CTAs per SM).  Reductions over channels (grad_B, grad_C) are done in
 // registers with a fixed reduce-scatter butterfly, across warps through shared memory and across
 // channel blocks / batch rows through partial buffers summed in a fixed order: no atomics, so
 // results are bitwise reproducible.
@@ -62,8 +63,38 @@ __device__ __forceinline__ float ex2_fast(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
-// softplus with PyTorch's threshold (x > 20 -> x)
-__device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(__expf(x)); }
+// softplus with PyTorch's threshold (x > 20 -> x).  log1p(e) as a 6-term alternating series for
+// e < 0.1 (truncation below 2e-7 relative) and log(1 + e) above, where rounding 1 + e costs at
+// most 6e-7 relative: full float32 accuracy for two special-function ops.
+__device__ __forceinline__ float softplus_f(float x) {
+    if (x > 20.f) return x;
+    const float e = __expf(x);
+    if (e < 0.1f) {
+        float p = fmaf(e, -1.f / 6.f, 0.2f);
+        p = fmaf(e, p, -0.25f);
+        p = fmaf(e, p, 1.f / 3.f);
+        p = fmaf(e, p, -0.5f);
+        p = fmaf(e, p, 1.f);
+        return e * p;
+    }
+    return __logf(1.f + e);
+}
+
+// Sum v[0..G) over the TPC lanes of a channel group so that lane `ng` ends with the total of
+// v[ng] in v[0] (G == TPC): log2(TPC) exchange steps moving G/2, G/4, ... values each.
+template <int TPC>
+__device__ __forceinline__ void group_reduce_scatter(float (&v)[TPC], int ng) {
+#pragma unroll
+    for (int off = TPC / 2; off >= 1; off >>= 1) {
+        const bool upper = (ng & off) != 0;
+#pragma unroll
+        for (int i = 0; i < off; ++i) {
+            const float send = upper ? v[i] : v[i + off];
+            const float keep = upper ? v[i + off] : v[i];
+            v[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+        }
+    }
+}
 __device__ __forceinline__ float sigmoid_f(float x) { return __fdividef(1.f, 1.f + __expf(-x)); }
 
 // Copy a [rows x cols] float block (row pitch `pitch` in global memory, rows below `rows_live`
@@ -174,10 +205,10 @@ __global__ void __launch_bounds__(DB* TPC) mamba_fwd_kernel(const MambaArgs p) {
         float* ob = outbuf + (c & 1) * kT * DB;
         const float* Bs = st + 3 * kT * DB + n0;
         const float* Cs = Bs + kT * NPAD;
-        for (int t = 0; t < tlive; ++t) {
+        // one time step of this thread's 4 states; returns its share of y_t = h_t . C_t
+        auto state_step = [&](int t) -> float {
             const float delta = st[t * DB + dl];
-            const float uu = st[kT * DB + t * DB + dl];
-            const float du = delta * uu;
+            const float du = delta * st[kT * DB + t * DB + dl];
             const float4 Bv = *reinterpret_cast<const float4*>(Bs + t * NPAD);
             const float4 Cv = *reinterpret_cast<const float4*>(Cs + t * NPAD);
             const float bq[kNPT] = {Bv.x, Bv.y, Bv.z, Bv.w}, cq[kNPT] = {Cv.x, Cv.y, Cv.z, Cv.w};
@@ -188,9 +219,34 @@ __global__ void __launch_bounds__(DB* TPC) mamba_fwd_kernel(const MambaArgs p) {
                 h[q] = fmaf(lam, h[q], __fmul_rn(du, bq[q]));
                 yp = fmaf(h[q], cq[q], yp);
             }
+            return yp;
+        };
+        auto emit = [&](int t, float y) {  // gated output of step t for this thread's channel
+            ob[t * DB + dl] = (y + Dp * st[kT * DB + t * DB + dl]) * st[2 * kT * DB + t * DB + dl];
+        };
+        constexpr int G = (TPC >= 2 && TPC <= kT) ? TPC : 1;  // steps whose y sums are reduced together
+        if (tlive == kT) {
 #pragma unroll
-            for (int off = 1; off < TPC; off <<= 1) yp += __shfl_xor_sync(0xffffffffu, yp, off);
-            if (ng == 0) ob[t * DB + dl] = (yp + Dp * uu) * st[2 * kT * DB + t * DB + dl];
+            for (int tg = 0; tg < kT; tg += G) {
+                float yv[G];
+#pragma unroll
+                for (int k = 0; k < G; ++k) yv[k] = state_step(tg + k);
+                if constexpr (G > 1) {
+                    group_reduce_scatter<G>(yv, ng);  // lane ng now owns step tg + ng
+                    emit(tg + ng, yv[0]);
+                } else {
+#pragma unroll
+                    for (int off = 1; off < TPC; off <<= 1) yv[0] += __shfl_xor_sync(0xffffffffu, yv[0], off);
+                    if (ng == 0) emit(tg, yv[0]);
+                }
+            }
+        } else {
+            for (int t = 0; t < tlive; ++t) {
+                float yp = state_step(t);
+#pragma unroll
+                for (int off = 1; off < TPC; off <<= 1) yp += __shfl_xor_sync(0xffffffffu, yp, off);
+                if (ng == 0) emit(t, yp);
+            }
         }
         if constexpr (STORE_CHK) {
             if (tlive == kT && d_ok) {
@@ -236,19 +292,18 @@ __device__ __forceinline__ void rs_step(float (&v)[8], int lane) {
 }
 
 template <int TPC, int DB, int VEC, int S>
-__global__ void __launch_bounds__(DB* TPC) mamba_bwd_kernel(const MambaArgs p) {
+__global__ void __launch_bounds__(DB* TPC, 3) mamba_bwd_kernel(const MambaArgs p) {
     constexpr int NTHR = DB * TPC;
     constexpr int NW = NTHR / 32;
     constexpr int NPAD = kNPT * TPC;
     constexpr int TD = kT * DB;
     constexpr int STAGE = 4 * TD + 2 * kT * NPAD + 4 * NTHR;  // draw,u,z,gout | Bt,Ct | checkpoint
+    constexpr int G = (TPC >= 2 && TPC <= kT) ? TPC : 1;       // steps whose channel sums are reduced together
     extern __shared__ __align__(16) float smem[];
-    float* ring = smem;                          // [S][STAGE]
-    float* sigd = ring + S * STAGE;              // [kT][DB]   sigmoid(draw)
-    float* obuf = sigd + TD;                     // [3][kT][DB] staged gdraw, gu, gz
-    float* red = obuf + 3 * TD;                  // [NW][kT][2][NPAD] per-warp grad_B / grad_C rows
-    float4* hbuf = reinterpret_cast<float4*>(red + NW * kT * 2 * NPAD);  // [kT][NTHR] states
-    float4* lbuf = hbuf + kT * NTHR;                                      // [kT][NTHR] decays
+    float* ring = smem;              // [S][STAGE]
+    float* sigd = ring + S * STAGE;  // [kT][DB]   sigmoid(draw)
+    float* obuf = sigd + TD;         // [3][kT][DB] staged gdraw, gu, gz
+    float* red = obuf + 3 * TD;      // [NW][kT][2][NPAD] per-warp grad_B / grad_C rows
 
     const int tid = threadIdx.x;
     const int lane = tid & 31, wid = tid >> 5;
@@ -299,13 +354,13 @@ __global__ void __launch_bounds__(DB* TPC) mamba_bwd_kernel(const MambaArgs p) {
         mcp_commit();
     }
 
-    float A1[kNPT], A2[kNPT], G[kNPT], gA[kNPT], lam_next[kNPT];
+    float A1[kNPT], A2[kNPT], Gs[kNPT], gA[kNPT], lam_next[kNPT];
 #pragma unroll
     for (int q = 0; q < kNPT; ++q) {
         const bool ok = d_ok && (n0 + q) < N;
         A1[q] = ok ? p.A[d * N + n0 + q] : 0.f;
         A2[q] = A1[q] * kLog2e;
-        G[q] = (ok && p.ghlast != nullptr) ? p.ghlast[(b * D + d) * N + n0 + q] : 0.f;
+        Gs[q] = (ok && p.ghlast != nullptr) ? p.ghlast[(b * D + d) * N + n0 + q] : 0.f;
         gA[q] = 0.f;
         lam_next[q] = 1.f;  // passes ghlast into G_{L-1} unchanged
     }
@@ -337,66 +392,55 @@ __global__ void __launch_bounds__(DB* TPC) mamba_bwd_kernel(const MambaArgs p) {
 
         const float* Bs = st + 4 * TD + n0;
         const float* Cs = Bs + kT * NPAD;
-        // recompute the tile's states and decays from its start state
-        float h[kNPT];
+        // recompute the tile's states from its start state, kept in registers
+        float hreg[kT][kNPT];
         {
+            float h[kNPT];
             const float* ck = st + 4 * TD + 2 * kT * NPAD + 4 * tid;
             const bool have = d_ok && (c > 0 || first_has_h0);
 #pragma unroll
             for (int q = 0; q < kNPT; ++q) h[q] = (have && n0 + q < N) ? ck[q] : 0.f;
-        }
-        for (int t = 0; t < tlive; ++t) {
-            const float delta = st[t * DB + dl];
-            const float du = delta * st[TD + t * DB + dl];
-            const float4 Bv = *reinterpret_cast<const float4*>(Bs + t * NPAD);
-            const float bq[kNPT] = {Bv.x, Bv.y, Bv.z, Bv.w};
-            float lam[kNPT];
 #pragma unroll
-            for (int q = 0; q < kNPT; ++q) {
-                lam[q] = ex2_fast(delta * A2[q]);
-                h[q] = fmaf(lam[q], h[q], __fmul_rn(du, bq[q]));
+            for (int t = 0; t < kT; ++t) {
+                if (t < tlive) {
+                    const float delta = st[t * DB + dl];
+                    const float du = delta * st[TD + t * DB + dl];
+                    const float4 Bv = *reinterpret_cast<const float4*>(Bs + t * NPAD);
+                    const float bq[kNPT] = {Bv.x, Bv.y, Bv.z, Bv.w};
+#pragma unroll
+                    for (int q = 0; q < kNPT; ++q)
+                        h[q] = fmaf(ex2_fast(delta * A2[q]), h[q], __fmul_rn(du, bq[q]));
+                }
+#pragma unroll
+                for (int q = 0; q < kNPT; ++q) hreg[t][q] = h[q];
             }
-            hbuf[t * NTHR + tid] = make_float4(h[0], h[1], h[2], h[3]);
-            lbuf[t * NTHR + tid] = make_float4(lam[0], lam[1], lam[2], lam[3]);
         }
 
-        // reverse sweep
-        for (int t = tlive - 1; t >= 0; --t) {
+        // one step of the reverse sweep for this thread's 4 states: updates G, grad_A, the
+        // per-warp grad_B / grad_C rows, and returns this thread's shares of y, grad_delta and the
+        // B-weighted sum that goes into grad_u
+        auto sweep_step = [&](int t, const float (&hv)[kNPT], float& yp, float& gdp, float& gus) {
             const float delta = st[t * DB + dl];
             const float uu = st[TD + t * DB + dl];
             const float gy = st[2 * TD + t * DB + dl];
             const float du = delta * uu;
             const float4 Bv = *reinterpret_cast<const float4*>(Bs + t * NPAD);
             const float4 Cv = *reinterpret_cast<const float4*>(Cs + t * NPAD);
-            const float4 hv4 = hbuf[t * NTHR + tid];
             const float bq[kNPT] = {Bv.x, Bv.y, Bv.z, Bv.w}, cq[kNPT] = {Cv.x, Cv.y, Cv.z, Cv.w};
-            const float hv[kNPT] = {hv4.x, hv4.y, hv4.z, hv4.w};
-            float yp = 0.f, gdp = 0.f, gus = 0.f;
+            yp = 0.f, gdp = 0.f, gus = 0.f;
             float vals[8];
 #pragma unroll
             for (int q = 0; q < kNPT; ++q) {
                 yp = fmaf(hv[q], cq[q], yp);
-                G[q] = fmaf(lam_next[q], G[q], gy * cq[q]);
+                Gs[q] = fmaf(lam_next[q], Gs[q], gy * cq[q]);
                 // lam_t h_{t-1} = h_t - v_t, with v_t rounded exactly as in the recurrence (so 0 stays 0)
                 const float lhp = __fsub_rn(hv[q], __fmul_rn(du, bq[q]));
-                vals[q] = G[q] * du;                   // grad_B contribution
-                vals[4 + q] = gy * hv[q];              // grad_C contribution
-                gA[q] = fmaf(G[q] * lhp, delta, gA[q]);
-                gdp = fmaf(G[q], fmaf(A1[q], lhp, uu * bq[q]), gdp);
-                gus = fmaf(G[q], bq[q], gus);
-            }
-#pragma unroll
-            for (int off = 1; off < TPC; off <<= 1) {
-                yp += __shfl_xor_sync(0xffffffffu, yp, off);
-                gdp += __shfl_xor_sync(0xffffffffu, gdp, off);
-                gus += __shfl_xor_sync(0xffffffffu, gus, off);
-            }
-            if (ng == 0) {
-                const float y = yp + Dp * uu;
-                obuf[t * DB + dl] = gdp * sigd[t * DB + dl];
-                obuf[TD + t * DB + dl] = fmaf(delta, gus, gy * Dp);
-                obuf[2 * TD + t * DB + dl] = st[3 * TD + t * DB + dl] * y;
-                gDp = fmaf(gy, uu, gDp);
+                vals[q] = Gs[q] * du;       // grad_B contribution
+                vals[4 + q] = gy * hv[q];   // grad_C contribution
+                gA[q] = fmaf(Gs[q] * lhp, delta, gA[q]);
+                gdp = fmaf(Gs[q], fmaf(A1[q], lhp, uu * bq[q]), gdp);
+                gus = fmaf(Gs[q], bq[q], gus);
+                lam_next[q] = ex2_fast(delta * A2[q]);  // lam_t, the decay the step before will need
             }
             // sum the 8 values over the channels of this warp; lanes end up owning distinct rows
             if constexpr (TPC <= 16) rs_step<16, 8>(vals, lane);
@@ -404,24 +448,56 @@ __global__ void __launch_bounds__(DB* TPC) mamba_bwd_kernel(const MambaArgs p) {
             if constexpr (TPC <= 4) rs_step<4, 2>(vals, lane);
             if constexpr (TPC <= 2) rs_step<2, 1>(vals, lane);
             if constexpr (TPC <= 1) rs_step<1, 1>(vals, lane);
-            {
-                constexpr int CNT = TPC >= 32 ? 8 : (TPC == 16 ? 4 : (TPC == 8 ? 2 : 1));
-                int base = 0;
-                if (TPC <= 16) base += (lane & 16) ? 4 : 0;
-                if (TPC <= 8) base += (lane & 8) ? 2 : 0;
-                if (TPC <= 4) base += (lane & 4) ? 1 : 0;
-                const bool writer = TPC > 2 || (TPC == 2 ? (lane & 2) == 0 : (lane & 3) == 0);
-                if (writer) {
-                    float* r = red + (wid * kT + t) * 2 * NPAD;
+            constexpr int CNT = TPC >= 32 ? 8 : (TPC == 16 ? 4 : (TPC == 8 ? 2 : 1));
+            int base = 0;
+            if (TPC <= 16) base += (lane & 16) ? 4 : 0;
+            if (TPC <= 8) base += (lane & 8) ? 2 : 0;
+            if (TPC <= 4) base += (lane & 4) ? 1 : 0;
+            const bool writer = TPC > 2 || (TPC == 2 ? (lane & 2) == 0 : (lane & 3) == 0);
+            if (writer) {
+                float* r = red + (wid * kT + t) * 2 * NPAD;
 #pragma unroll
-                    for (int k = 0; k < CNT; ++k) {
-                        const int idx = base + k;
-                        r[(idx >> 2) * NPAD + n0 + (idx & 3)] = vals[k];
-                    }
+                for (int k = 0; k < CNT; ++k) {
+                    const int idx = base + k;
+                    r[(idx >> 2) * NPAD + n0 + (idx & 3)] = vals[k];
                 }
             }
-            const float4 l4 = lbuf[t * NTHR + tid];
-            lam_next[0] = l4.x, lam_next[1] = l4.y, lam_next[2] = l4.z, lam_next[3] = l4.w;
+        };
+        // finish the per-(t, d) gradients of step t from the channel-group sums
+        auto finish = [&](int t, float y_sum, float gd_sum, float gu_sum) {
+            const float delta = st[t * DB + dl];
+            const float uu = st[TD + t * DB + dl];
+            const float gy = st[2 * TD + t * DB + dl];
+            obuf[t * DB + dl] = gd_sum * sigd[t * DB + dl];
+            obuf[TD + t * DB + dl] = fmaf(delta, gu_sum, gy * Dp);
+            obuf[2 * TD + t * DB + dl] = st[3 * TD + t * DB + dl] * fmaf(Dp, uu, y_sum);
+            gDp = fmaf(gy, uu, gDp);
+        };
+
+#pragma unroll
+        for (int tg = kT - G; tg >= 0; tg -= G) {
+            float yv[G], gdv[G], guv[G];
+#pragma unroll
+            for (int k = G - 1; k >= 0; --k) {
+                yv[k] = 0.f, gdv[k] = 0.f, guv[k] = 0.f;
+                if (tg + k < tlive) sweep_step(tg + k, hreg[tg + k], yv[k], gdv[k], guv[k]);
+            }
+            if (tg < tlive) {
+                if constexpr (G > 1) {
+                    group_reduce_scatter<G>(yv, ng);  // lane ng now owns step tg + ng
+                    group_reduce_scatter<G>(gdv, ng);
+                    group_reduce_scatter<G>(guv, ng);
+                    if (tg + ng < tlive) finish(tg + ng, yv[0], gdv[0], guv[0]);
+                } else {
+#pragma unroll
+                    for (int off = 1; off < TPC; off <<= 1) {
+                        yv[0] += __shfl_xor_sync(0xffffffffu, yv[0], off);
+                        gdv[0] += __shfl_xor_sync(0xffffffffu, gdv[0], off);
+                        guv[0] += __shfl_xor_sync(0xffffffffu, guv[0], off);
+                    }
+                    if (ng == 0) finish(tg, yv[0], gdv[0], guv[0]);
+                }
+            }
         }
         __syncthreads();
 
@@ -450,11 +526,11 @@ __global__ void __launch_bounds__(DB* TPC) mamba_bwd_kernel(const MambaArgs p) {
                 const int t = e / (2 * NPAD), rem = e - t * 2 * NPAD;
                 const int which = rem / NPAD, n = rem - which * NPAD;
                 if (n < N) {
-                    float s = 0.f;
+                    float sacc = 0.f;
 #pragma unroll
-                    for (int ww = 0; ww < NW; ++ww) s += red[(ww * kT + t) * 2 * NPAD + rem];
+                    for (int ww = 0; ww < NW; ++ww) sacc += red[(ww * kT + t) * 2 * NPAD + rem];
                     float* dst = which == 0 ? p.gB_part : p.gC_part;
-                    dst[((dblk * p.B + b) * L + t0 + t) * N + n] = s;
+                    dst[((dblk * p.B + b) * L + t0 + t) * N + n] = sacc;
                 }
             }
         }
@@ -462,12 +538,15 @@ __global__ void __launch_bounds__(DB* TPC) mamba_bwd_kernel(const MambaArgs p) {
     }
     mcp_wait<0>();
 
+    // grad_Dp: every lane of a channel group summed the steps it finished
+#pragma unroll
+    for (int off = 1; off < TPC; off <<= 1) gDp += __shfl_xor_sync(0xffffffffu, gDp, off);
     if (d_ok) {
 #pragma unroll
         for (int q = 0; q < kNPT; ++q) {
             if (n0 + q < N) {
                 p.gA_part[(b * D + d) * N + n0 + q] = gA[q];
-                if (p.gh0 != nullptr) p.gh0[(b * D + d) * N + n0 + q] = lam_next[q] * G[q];
+                if (p.gh0 != nullptr) p.gh0[(b * D + d) * N + n0 + q] = lam_next[q] * Gs[q];
             }
         }
         if (ng == 0) p.gDp_part[b * D + d] = gDp;
@@ -489,7 +568,7 @@ __global__ void sum_leading_kernel(const float* __restrict__ in, float* __restri
 #define MAMBA_FWD_S 4  // ring stages of the forward
 #endif
 #ifndef MAMBA_BWD_S
-#define MAMBA_BWD_S 2  // ring stages of the adjoint (its state buffers take most of shared memory)
+#define MAMBA_BWD_S 3  // ring stages of the adjoint
 #endif
 constexpr int kMambaThreads = 128;
 
@@ -529,9 +608,8 @@ static int launch_mamba_fwd(const MambaArgs& a, cudaStream_t st) {
 template <int TPC, int VEC>
 static int launch_mamba_bwd(const MambaArgs& a, cudaStream_t st) {
     constexpr int DB = kMambaThreads / TPC, S = MAMBA_BWD_S, NPAD = kNPT * TPC, NW = kMambaThreads / 32;
-    constexpr size_t smem =
-        sizeof(float) * ((size_t)S * (4 * kT * DB + 2 * kT * NPAD + 4 * kMambaThreads) + 4 * kT * DB +
-                         NW * kT * 2 * NPAD + 2 * kT * kMambaThreads * 4);
+    constexpr size_t smem = sizeof(float) * ((size_t)S * (4 * kT * DB + 2 * kT * NPAD + 4 * kMambaThreads) +
+                                             4 * kT * DB + NW * kT * 2 * NPAD);
     auto kern = mamba_bwd_kernel<TPC, DB, VEC, S>;
     static bool configured[64] = {false};
     if (set_smem(kern, smem, configured) != B200_OK) return B200_ERR_LAUNCH;
