@@ -63,8 +63,8 @@ int b200_diag_bwd(int dtype, int64_t M, int64_t L, int64_t N, const void* g, con
  * 4 MiB array inside the library image (held by every GPU that loads the library until exit).
  * Limits and rules:
  *  - problems whose look-back state exceeds 4 MiB are refused with B200_ERR_UNSUPPORTED
- *    (b200_diag_workspace_bytes(dtype, 0, M, L, N) > 4194304; roughly M * ceil(N/64..128) *
- *    ceil(L/32) <= 2700 tiles, e.g. 16 x 1000 x 64 complex fits);
+ *    (b200_diag_workspace_bytes(dtype, 0, M, L, N) > 4194304; a tile is about 100 steps of 64 to
+ *    128 lanes and roughly 2700 tiles fit, e.g. 16 x 1000 x 64 complex uses 176 of them);
  *  - the first call on each device looks up the array's device address (cudaGetSymbolAddress)
  *    with that device current; make that first call before any stream capture;
  *  - every call reuses the one array (it zeroes the words that must start at zero itself), so two

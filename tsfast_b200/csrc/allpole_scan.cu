@@ -327,18 +327,18 @@ __global__ void __launch_bounds__(32 * W) allpole_kernel(const AllpoleArgs p) {
 
 // ------------------------------------------------------------------------------- host side
 #ifndef ALLPOLE_W
-#define ALLPOLE_W 4  // lanes (warps) per CTA
+#define ALLPOLE_W 8  // lanes (warps) per CTA for orders up to 8, half of it above
 #endif
 #ifndef ALLPOLE_FWD_S
-#define ALLPOLE_FWD_S 6  // ring stages per warp
+#define ALLPOLE_FWD_S 4  // ring stages per warp
 #endif
 #ifndef ALLPOLE_BWD_S
-#define ALLPOLE_BWD_S 4
+#define ALLPOLE_BWD_S 3
 #endif
 
 template <int NA, bool BWD, int VEC>
 static int launch_allpole(const AllpoleArgs& a, cudaStream_t st) {
-    constexpr int W = ALLPOLE_W;
+    constexpr int W = NA <= 8 ? ALLPOLE_W : ALLPOLE_W / 2;  // high orders: the matrix powers take the shared memory
     constexpr int S = BWD ? ALLPOLE_BWD_S : ALLPOLE_FWD_S;
     constexpr int NTENS = BWD ? 2 : 1;
     constexpr size_t smem = (size_t)W * (7 * NA * NA * sizeof(double) + (size_t)S * NTENS * kStageF * sizeof(float));

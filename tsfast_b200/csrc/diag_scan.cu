@@ -688,10 +688,10 @@ __global__ void __launch_bounds__(32 * W, MINB) diag_stream_kernel(const DiagArg
 // warps along time and a ring of DIAG_*_S tiles in shared memory, and DIAG_*_MINB CTAs are
 // asked to fit one SM.  The macros exist so that tuning builds can sweep them.
 #ifndef DIAG_FWD_BYTES
-#define DIAG_FWD_BYTES 64
+#define DIAG_FWD_BYTES 256
 #endif
 #ifndef DIAG_BWD_BYTES
-#define DIAG_BWD_BYTES 64
+#define DIAG_BWD_BYTES 128
 #endif
 #ifndef DIAG_FWD_W
 #define DIAG_FWD_W 8
@@ -700,13 +700,13 @@ __global__ void __launch_bounds__(32 * W, MINB) diag_stream_kernel(const DiagArg
 #define DIAG_BWD_W 8
 #endif
 #ifndef DIAG_FWD_S
-#define DIAG_FWD_S 3
+#define DIAG_FWD_S 2
 #endif
 #ifndef DIAG_BWD_S
-#define DIAG_BWD_S 3
+#define DIAG_BWD_S 2
 #endif
 #ifndef DIAG_FWD_MINB
-#define DIAG_FWD_MINB 2
+#define DIAG_FWD_MINB 1
 #endif
 #ifndef DIAG_BWD_MINB
 #define DIAG_BWD_MINB 1
@@ -715,14 +715,23 @@ __global__ void __launch_bounds__(32 * W, MINB) diag_stream_kernel(const DiagArg
 #define DIAG_MAX_VEC_BYTES 16  // widest access per thread and step
 #endif
 
+// Steps per thread: the byte budget, at most 16 (unrolled), and small enough that the ring of the
+// widest instantiation (two streamed tensors forward, three in the adjoint) stays under 192 KB.
+constexpr int diag_ts(int pack_bytes, bool bwd) {
+    const int w = bwd ? DIAG_BWD_W : DIAG_FWD_W, st = bwd ? DIAG_BWD_S : DIAG_FWD_S, nt = bwd ? 3 : 2;
+    int ts = (bwd ? DIAG_BWD_BYTES : DIAG_FWD_BYTES) / pack_bytes;
+    const int cap = 196608 / (st * nt * 32 * w * pack_bytes);
+    if (ts > cap) ts = cap;
+    if (ts > 16) ts = 16;
+    return ts < 1 ? 1 : ts;
+}
+
 template <typename E, int V, bool BWD>
 struct Cfg {
     static constexpr int W = BWD ? DIAG_BWD_W : DIAG_FWD_W;
     static constexpr int S = BWD ? DIAG_BWD_S : DIAG_FWD_S;
     static constexpr int MINB = BWD ? DIAG_BWD_MINB : DIAG_FWD_MINB;
-    static constexpr int TSraw = (BWD ? DIAG_BWD_BYTES : DIAG_FWD_BYTES) / (int)(sizeof(E) * V);
-    static constexpr int TS = TSraw > 16 ? 16 : TSraw;  // narrow vectors: cap the unrolled steps
-    static_assert(TS >= 1, "tile bytes too small for this vector width");
+    static constexpr int TS = diag_ts((int)(sizeof(E) * V), BWD);
 };
 
 struct DiagPlan {
@@ -736,8 +745,7 @@ static DiagPlan make_plan(int dtype, int V, bool bwd, bool needs_part, long long
     const size_t esz = dtype == B200_C64 ? 8 : 4;
     pl.V = V;
     pl.W = bwd ? DIAG_BWD_W : DIAG_FWD_W;
-    pl.TS = (bwd ? DIAG_BWD_BYTES : DIAG_FWD_BYTES) / (int)(esz * V);
-    if (pl.TS > 16) pl.TS = 16;
+    pl.TS = diag_ts((int)(esz * V), bwd);
     const long long NL = 32LL * V, TT = (long long)pl.TS * pl.W;
     pl.C = (L + TT - 1) / TT;
     pl.J = (N + NL - 1) / NL;

@@ -14,12 +14,12 @@
 // gate once per (t, d), then the state loop runs from shared memory and the gated outputs leave
 // through a staging tile as coalesced 16-byte stores.
 //
-// Training: the forward also writes the state every kT steps (chk [B, ceil(L/kT), D, N], slot k =
-// state after step (k+1)*kT - 1), 1/16 of a full state store.  The adjoint walks the tiles in
-// reverse: it recomputes the tile's 16 states per thread from the checkpoint into registers, then
+// Training: the forward also writes the state every kTB = 8 steps (chk [B, ceil(L/8), D, N], slot k =
+// state after step 8(k+1) - 1), 1/8 of a full state store.  The adjoint walks the tiles in
+// reverse: it recomputes the tile's 8 states per thread from the checkpoint into registers, then
 // sweeps the tile backwards running G_t = gy_t C_t + lam_{t+1} G_{t+1} (the decays are evaluated
 // again on the way back: two exps per state and step, which buys the registers/shared memory for
-// three CTAs per SM).  Reductions over channels (grad_B, grad_C) are done in
+// four CTAs per SM, i.e. the whole grid of the benchmark shape in one wave).  Reductions over channels (grad_B, grad_C) are done in
 // registers with a fixed reduce-scatter butterfly, across warps through shared memory and across
 // channel blocks / batch rows through partial buffers summed in a fixed order: no atomics, so
 // results are bitwise reproducible.
@@ -29,7 +29,8 @@
 
 namespace b200 {
 
-constexpr int kT = 16;       // steps per tile == checkpoint interval
+constexpr int kT = 16;       // steps per forward tile
+constexpr int kTB = 8;       // checkpoint interval == steps per adjoint tile (its states live in registers)
 constexpr int kNPT = 4;      // states per thread
 constexpr float kLog2e = 1.4426950408889634f;
 
@@ -41,7 +42,7 @@ struct MambaArgs {
     float *gdraw, *gu, *gz, *gh0;
     float *gA_part, *gDp_part, *gB_part, *gC_part;  // [B,D,N], [B,D], [ndb,B,L,N] x2
     long long B, L, D, N;
-    long long ndb, NC;  // channel blocks per row, tiles per sequence
+    long long ndb, NC, NCB;  // channel blocks per row, forward tiles, checkpoint slots (= adjoint tiles)
 };
 
 __device__ __forceinline__ void mcp16(void* smem_dst, const void* gsrc) {
@@ -225,12 +226,30 @@ __global__ void __launch_bounds__(DB* TPC) mamba_fwd_kernel(const MambaArgs p) {
             ob[t * DB + dl] = (y + Dp * st[kT * DB + t * DB + dl]) * st[2 * kT * DB + t * DB + dl];
         };
         constexpr int G = (TPC >= 2 && TPC <= kT) ? TPC : 1;  // steps whose y sums are reduced together
+        auto store_chk = [&](int t_done) {  // state after step t_done (tile-local) -> its checkpoint slot
+            if constexpr (STORE_CHK) {
+                if (d_ok) {
+                    const long long slot_k = (c * kT + t_done + 1) / kTB - 1;
+                    float* ck = p.chk + ((b * p.NCB + slot_k) * D + d) * N + n0;
+                    if (VEC == 4 && n0 + kNPT <= N) {
+                        *reinterpret_cast<float4*>(ck) = make_float4(h[0], h[1], h[2], h[3]);
+                    } else {
+#pragma unroll
+                        for (int q = 0; q < kNPT; ++q)
+                            if (n0 + q < N) ck[q] = h[q];
+                    }
+                }
+            }
+        };
         if (tlive == kT) {
 #pragma unroll
             for (int tg = 0; tg < kT; tg += G) {
                 float yv[G];
 #pragma unroll
-                for (int k = 0; k < G; ++k) yv[k] = state_step(tg + k);
+                for (int k = 0; k < G; ++k) {
+                    yv[k] = state_step(tg + k);
+                    if ((tg + k + 1) % kTB == 0) store_chk(tg + k);
+                }
                 if constexpr (G > 1) {
                     group_reduce_scatter<G>(yv, ng);  // lane ng now owns step tg + ng
                     emit(tg + ng, yv[0]);
@@ -243,21 +262,10 @@ __global__ void __launch_bounds__(DB* TPC) mamba_fwd_kernel(const MambaArgs p) {
         } else {
             for (int t = 0; t < tlive; ++t) {
                 float yp = state_step(t);
+                if ((t + 1) % kTB == 0) store_chk(t);
 #pragma unroll
                 for (int off = 1; off < TPC; off <<= 1) yp += __shfl_xor_sync(0xffffffffu, yp, off);
                 if (ng == 0) emit(t, yp);
-            }
-        }
-        if constexpr (STORE_CHK) {
-            if (tlive == kT && d_ok) {
-                float* ck = p.chk + ((b * p.NC + c) * D + d) * N + n0;
-                if (VEC == 4 && n0 + kNPT <= N) {
-                    *reinterpret_cast<float4*>(ck) = make_float4(h[0], h[1], h[2], h[3]);
-                } else {
-#pragma unroll
-                    for (int q = 0; q < kNPT; ++q)
-                        if (n0 + q < N) ck[q] = h[q];
-                }
             }
         }
     }
@@ -292,18 +300,18 @@ __device__ __forceinline__ void rs_step(float (&v)[8], int lane) {
 }
 
 template <int TPC, int DB, int VEC, int S>
-__global__ void __launch_bounds__(DB* TPC, 3) mamba_bwd_kernel(const MambaArgs p) {
+__global__ void __launch_bounds__(DB* TPC, 4) mamba_bwd_kernel(const MambaArgs p) {
     constexpr int NTHR = DB * TPC;
     constexpr int NW = NTHR / 32;
     constexpr int NPAD = kNPT * TPC;
-    constexpr int TD = kT * DB;
-    constexpr int STAGE = 4 * TD + 2 * kT * NPAD + 4 * NTHR;  // draw,u,z,gout | Bt,Ct | checkpoint
-    constexpr int G = (TPC >= 2 && TPC <= kT) ? TPC : 1;       // steps whose channel sums are reduced together
+    constexpr int TD = kTB * DB;
+    constexpr int STAGE = 4 * TD + 2 * kTB * NPAD + 4 * NTHR;  // draw,u,z,gout | Bt,Ct | checkpoint
+    constexpr int G = (TPC >= 2 && TPC <= kTB) ? TPC : 1;       // steps whose channel sums are reduced together
     extern __shared__ __align__(16) float smem[];
     float* ring = smem;              // [S][STAGE]
-    float* sigd = ring + S * STAGE;  // [kT][DB]   sigmoid(draw)
-    float* obuf = sigd + TD;         // [3][kT][DB] staged gdraw, gu, gz
-    float* red = obuf + 3 * TD;      // [NW][kT][2][NPAD] per-warp grad_B / grad_C rows
+    float* sigd = ring + S * STAGE;  // [kTB][DB]   sigmoid(draw)
+    float* obuf = sigd + TD;         // [3][kTB][DB] staged gdraw, gu, gz
+    float* red = obuf + 3 * TD;      // [NW][kTB][2][NPAD] per-warp grad_B / grad_C rows
 
     const int tid = threadIdx.x;
     const int lane = tid & 31, wid = tid >> 5;
@@ -317,13 +325,13 @@ __global__ void __launch_bounds__(DB* TPC, 3) mamba_bwd_kernel(const MambaArgs p
     const bool d_ok = d < D;
     const int dcols = (int)((D - d0) < DB ? (D - d0) : DB);
 
-    for (int e = tid; e < S * STAGE + 4 * TD + NW * kT * 2 * NPAD; e += NTHR) smem[e] = 0.f;
+    for (int e = tid; e < S * STAGE + 4 * TD + NW * kTB * 2 * NPAD; e += NTHR) smem[e] = 0.f;
     __syncthreads();
 
     // tiles are visited from the last to the first: visit index i <-> tile c = NC-1-i
     auto issue = [&](long long c, int slot) {
-        const long long t0 = c * kT;
-        const int rows = (int)((L - t0) < kT ? (L - t0) : kT);
+        const long long t0 = c * kTB;
+        const int rows = (int)((L - t0) < kTB ? (L - t0) : kTB);
         float* st = ring + slot * STAGE;
         const long long off = (b * L + t0) * D + d0;
         copy_tile<VEC, NTHR>(st, DB, p.draw + off, D, rows, DB, dcols, tid);
@@ -332,10 +340,10 @@ __global__ void __launch_bounds__(DB* TPC, 3) mamba_bwd_kernel(const MambaArgs p
         copy_tile<VEC, NTHR>(st + 3 * TD, DB, p.gout + off, D, rows, DB, dcols, tid);
         const long long offn = (b * L + t0) * N;
         copy_tile<VEC, NTHR>(st + 4 * TD, NPAD, p.Bt + offn, N, rows, NPAD, (int)N, tid);
-        copy_tile<VEC, NTHR>(st + 4 * TD + kT * NPAD, NPAD, p.Ct + offn, N, rows, NPAD, (int)N, tid);
+        copy_tile<VEC, NTHR>(st + 4 * TD + kTB * NPAD, NPAD, p.Ct + offn, N, rows, NPAD, (int)N, tid);
         // this thread's start state of the tile: checkpoint slot c-1, or h0 for the first tile
-        float* ck = st + 4 * TD + 2 * kT * NPAD + 4 * tid;
-        const float* src = c > 0 ? p.chk + ((b * p.NC + c - 1) * D + d) * N + n0
+        float* ck = st + 4 * TD + 2 * kTB * NPAD + 4 * tid;
+        const float* src = c > 0 ? p.chk + ((b * p.NCB + c - 1) * D + d) * N + n0
                                  : (p.h0 != nullptr ? p.h0 + (b * D + d) * N + n0 : nullptr);
         if (d_ok && src != nullptr) {
             if (VEC == 4 && n0 + kNPT <= N) {
@@ -350,7 +358,7 @@ __global__ void __launch_bounds__(DB* TPC, 3) mamba_bwd_kernel(const MambaArgs p
 
 #pragma unroll
     for (int q = 0; q < S - 1; ++q) {
-        if (q < p.NC) issue(p.NC - 1 - q, q);
+        if (q < p.NCB) issue(p.NCB - 1 - q, q);
         mcp_commit();
     }
 
@@ -368,14 +376,14 @@ __global__ void __launch_bounds__(DB* TPC, 3) mamba_bwd_kernel(const MambaArgs p
     float gDp = 0.f;
     const bool first_has_h0 = p.h0 != nullptr;
 
-    for (long long i = 0; i < p.NC; ++i) {
-        const long long c = p.NC - 1 - i;
+    for (long long i = 0; i < p.NCB; ++i) {
+        const long long c = p.NCB - 1 - i;
         const int slot = (int)(i % S);
         float* st = ring + slot * STAGE;
-        const int tlive = (int)((L - c * kT) < kT ? (L - c * kT) : kT);
+        const int tlive = (int)((L - c * kTB) < kTB ? (L - c * kTB) : kTB);
         mcp_wait<S - 2>();
         __syncthreads();
-        if (i + S - 1 < p.NC) issue(p.NC - 1 - (i + S - 1), (int)((i + S - 1) % S));
+        if (i + S - 1 < p.NCB) issue(p.NCB - 1 - (i + S - 1), (int)((i + S - 1) % S));
         mcp_commit();
 
         // once per (t, d): delta, sigmoid(draw), gy = gout*silu(z), gq = gout*d silu(z)/dz
@@ -391,17 +399,17 @@ __global__ void __launch_bounds__(DB* TPC, 3) mamba_bwd_kernel(const MambaArgs p
         __syncthreads();
 
         const float* Bs = st + 4 * TD + n0;
-        const float* Cs = Bs + kT * NPAD;
+        const float* Cs = Bs + kTB * NPAD;
         // recompute the tile's states from its start state, kept in registers
-        float hreg[kT][kNPT];
+        float hreg[kTB][kNPT];
         {
             float h[kNPT];
-            const float* ck = st + 4 * TD + 2 * kT * NPAD + 4 * tid;
+            const float* ck = st + 4 * TD + 2 * kTB * NPAD + 4 * tid;
             const bool have = d_ok && (c > 0 || first_has_h0);
 #pragma unroll
             for (int q = 0; q < kNPT; ++q) h[q] = (have && n0 + q < N) ? ck[q] : 0.f;
 #pragma unroll
-            for (int t = 0; t < kT; ++t) {
+            for (int t = 0; t < kTB; ++t) {
                 if (t < tlive) {
                     const float delta = st[t * DB + dl];
                     const float du = delta * st[TD + t * DB + dl];
@@ -455,7 +463,7 @@ __global__ void __launch_bounds__(DB* TPC, 3) mamba_bwd_kernel(const MambaArgs p
             if (TPC <= 4) base += (lane & 4) ? 1 : 0;
             const bool writer = TPC > 2 || (TPC == 2 ? (lane & 2) == 0 : (lane & 3) == 0);
             if (writer) {
-                float* r = red + (wid * kT + t) * 2 * NPAD;
+                float* r = red + (wid * kTB + t) * 2 * NPAD;
 #pragma unroll
                 for (int k = 0; k < CNT; ++k) {
                     const int idx = base + k;
@@ -475,7 +483,7 @@ __global__ void __launch_bounds__(DB* TPC, 3) mamba_bwd_kernel(const MambaArgs p
         };
 
 #pragma unroll
-        for (int tg = kT - G; tg >= 0; tg -= G) {
+        for (int tg = kTB - G; tg >= 0; tg -= G) {
             float yv[G], gdv[G], guv[G];
 #pragma unroll
             for (int k = G - 1; k >= 0; --k) {
@@ -503,7 +511,7 @@ __global__ void __launch_bounds__(DB* TPC, 3) mamba_bwd_kernel(const MambaArgs p
 
         // staged per-(t,d) gradients -> global; per-warp grad_B/grad_C rows -> this block's partial
         {
-            const long long t0 = c * kT;
+            const long long t0 = c * kTB;
             constexpr int PPR = DB / VEC;
             float* dsts[3] = {p.gdraw, p.gu, p.gz};
 #pragma unroll
@@ -528,7 +536,7 @@ __global__ void __launch_bounds__(DB* TPC, 3) mamba_bwd_kernel(const MambaArgs p
                 if (n < N) {
                     float sacc = 0.f;
 #pragma unroll
-                    for (int ww = 0; ww < NW; ++ww) sacc += red[(ww * kT + t) * 2 * NPAD + rem];
+                    for (int ww = 0; ww < NW; ++ww) sacc += red[(ww * kTB + t) * 2 * NPAD + rem];
                     float* dst = which == 0 ? p.gB_part : p.gC_part;
                     dst[((dblk * p.B + b) * L + t0 + t) * N + n] = sacc;
                 }
@@ -608,8 +616,8 @@ static int launch_mamba_fwd(const MambaArgs& a, cudaStream_t st) {
 template <int TPC, int VEC>
 static int launch_mamba_bwd(const MambaArgs& a, cudaStream_t st) {
     constexpr int DB = kMambaThreads / TPC, S = MAMBA_BWD_S, NPAD = kNPT * TPC, NW = kMambaThreads / 32;
-    constexpr size_t smem = sizeof(float) * ((size_t)S * (4 * kT * DB + 2 * kT * NPAD + 4 * kMambaThreads) +
-                                             4 * kT * DB + NW * kT * 2 * NPAD);
+    constexpr size_t smem = sizeof(float) * ((size_t)S * (4 * kTB * DB + 2 * kTB * NPAD + 4 * kMambaThreads) +
+                                             4 * kTB * DB + NW * kTB * 2 * NPAD);
     auto kern = mamba_bwd_kernel<TPC, DB, VEC, S>;
     static bool configured[64] = {false};
     if (set_smem(kern, smem, configured) != B200_OK) return B200_ERR_LAUNCH;
@@ -702,7 +710,7 @@ static bool aligned16(std::initializer_list<const void*> ps) {
 
 extern "C" {
 
-int b200_mamba_chk_interval(void) { return b200::kT; }
+int b200_mamba_chk_interval(void) { return b200::kTB; }
 
 int b200_mamba_fwd(int64_t B, int64_t L, int64_t D, int64_t N, const void* draw, const void* A, const void* Bt,
                    const void* Ct, const void* u, const void* z, const void* Dp, const void* h0, void* out,
@@ -718,6 +726,7 @@ int b200_mamba_fwd(int64_t B, int64_t L, int64_t D, int64_t N, const void* draw,
     a.out = (float*)out, a.chk = (float*)chk, a.hlast = (float*)hlast;
     a.B = B, a.L = L, a.D = D, a.N = N;
     a.NC = (L + kT - 1) / kT;
+    a.NCB = (L + kTB - 1) / kTB;
     const bool vec = D % 4 == 0 && N % 4 == 0 && aligned16({draw, Bt, Ct, u, z, out, chk});
     return dispatch_mamba_fwd(tpc_for(N), chk != nullptr, vec, a, static_cast<cudaStream_t>(stream));
 }
@@ -738,7 +747,7 @@ int b200_mamba_bwd(int64_t B, int64_t L, int64_t D, int64_t N, const void* draw,
     if (B == 0 || D == 0) return B200_OK;
     if (!A || !Dp || !gA || !gDp || (h0 && !gh0)) return B200_ERR_ARG;
     if (L > 0 && (!draw || !Bt || !Ct || !u || !z || !gout || !gdraw || !gBt || !gCt || !gu || !gz)) return B200_ERR_ARG;
-    if (L > kT && !chk) return B200_ERR_ARG;
+    if (L > kTB && !chk) return B200_ERR_ARG;
     const MambaWs w = mamba_ws(B, L, D, N);
     if (!workspace || ((uintptr_t)workspace % 256) != 0 || workspace_bytes < w.total) return B200_ERR_WORKSPACE;
     char* base = static_cast<char*>(workspace);
@@ -753,6 +762,7 @@ int b200_mamba_bwd(int64_t B, int64_t L, int64_t D, int64_t N, const void* draw,
     a.B = B, a.L = L, a.D = D, a.N = N;
     a.ndb = w.ndb;
     a.NC = (L + kT - 1) / kT;
+    a.NCB = (L + kTB - 1) / kTB;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const bool vec = D % 4 == 0 && N % 4 == 0 && aligned16({draw, Bt, Ct, u, z, gout, chk, h0, gdraw, gu, gz});
     int rc = dispatch_mamba_bwd(tpc_for(N), vec, a, st);

@@ -8,7 +8,7 @@ Drop-in for the reference's ``tsfast/models/architectures/mamba/mamba_triton.py`
 the same three custom ops (inference, training with state checkpoints, backward) with fake
 implementations, under the ``b200scan`` namespace.  ``run`` is differentiable in all eight inputs
 and in ``h_last``.  The kernels are ``b200_mamba_fwd`` / ``b200_mamba_bwd`` of ``libb200scan.so``;
-the checkpoint interval is the library's (16 steps), not the reference's 8.
+the checkpoint interval (8 steps, as in the reference) is the library's: ``b200_mamba_chk_interval()``.
 """
 
 from __future__ import annotations
@@ -20,10 +20,14 @@ from . import _lib
 __all__ = ["supports", "run"]
 
 _MAX_N = 128
+_FAKE_CHK = 8  # checkpoint interval assumed by the fake (shape-only) implementations; checked against the library
 
 
 def _chk_interval() -> int:
-    return int(_lib.lib().b200_mamba_chk_interval())
+    k = int(_lib.lib().b200_mamba_chk_interval())
+    if k != _FAKE_CHK:
+        raise RuntimeError(f"libb200scan checkpoints every {k} steps, this module was written for {_FAKE_CHK}")
+    return k
 
 
 def supports(draw, A, Bt, Ct, u, z, Dp, h0) -> str | None:
@@ -103,7 +107,7 @@ def _fake_outs(draw, A, with_chk: bool):
     h_last = draw.new_empty(B, D, N)
     if not with_chk:
         return out, h_last
-    return out, h_last, draw.new_empty(B, -(-L // 16), D, N)
+    return out, h_last, draw.new_empty(B, -(-L // _FAKE_CHK), D, N)
 
 
 @_scan_op.register_fake
