@@ -118,6 +118,7 @@ def cpu_sample(seconds_target: float = 12.0, steps: int = 1, warmup: int = 1):
     from oracle import oracle as O
 
     O.build()
+    O.set_num_threads(len(os.sched_getaffinity(0)))  # torchrun exports OMP_NUM_THREADS=1; use every core we may
     rng = np.random.default_rng(0)
     rows = 8
     a = (1.0 / (1.0 + np.exp(-(rng.standard_normal((rows, T, D), dtype=np.float32) + 2.0)))).astype(np.float32)
@@ -493,6 +494,7 @@ def run_workload(args):
         if world == 1 and not args.no_cpu and not args.kernel_only:
             from oracle import oracle as O
             O.build()
+            O.set_num_threads(len(os.sched_getaffinity(0)))
             rows = wl["sample_rows"]
             sec, cnt = _time_cpu(wl["cpu"](rows), 1, 1, 10.0)
             base = {"value": round(step_bytes * rows / wl["rows"] / sec / 1e9, 3), "unit": "GB/s", "cores": O.num_threads(),
