@@ -80,8 +80,8 @@ __device__ __forceinline__ float iir_step(const float (&a)[NA], float (&s)[NA], 
     return y;
 }
 
-template <int NA, bool BWD, int VEC, int W, int S>
-__global__ void __launch_bounds__(32 * W) allpole_kernel(const AllpoleArgs p) {
+template <int NA, bool BWD, int VEC, int W, int S, int MINB>
+__global__ void __launch_bounds__(32 * W, MINB) allpole_kernel(const AllpoleArgs p) {
     static_assert(VEC == 4 || VEC == 1, "pieces are 16 or 4 bytes");
     constexpr int NTENS = BWD ? 2 : 1;
     constexpr int PIECES = kTile / VEC;  // copy pieces per tile and tensor
@@ -198,12 +198,14 @@ __global__ void __launch_bounds__(32 * W) allpole_kernel(const AllpoleArgs p) {
                 yv[4 * q] = u4.x, yv[4 * q + 1] = u4.y, yv[4 * q + 2] = u4.z, yv[4 * q + 3] = u4.w;
             }
         }
+        if (ph < 0 || ph + kTile > L) {  // edge tile only: steps outside the sequence get zero input
 #pragma unroll
-        for (int r = 0; r < kSeg; ++r) {  // steps outside the sequence: zero input, never stored
-            const bool okr = (tbase + r) >= 0 && (tbase + r) < L;
-            if (!okr) {
-                v[r] = 0.f;
-                if constexpr (BWD) yv[r] = 0.f;
+            for (int r = 0; r < kSeg; ++r) {
+                const bool okr = (tbase + r) >= 0 && (tbase + r) < L;
+                if (!okr) {
+                    v[r] = 0.f;
+                    if constexpr (BWD) yv[r] = 0.f;
+                }
             }
         }
         __syncwarp();  // everyone has read this stage before the next tile's copies may land in it
@@ -327,13 +329,19 @@ __global__ void __launch_bounds__(32 * W) allpole_kernel(const AllpoleArgs p) {
 
 // ------------------------------------------------------------------------------- host side
 #ifndef ALLPOLE_W
-#define ALLPOLE_W 8  // lanes (warps) per CTA for orders up to 8, half of it above
+#define ALLPOLE_W 4  // lanes (warps) per CTA for orders up to 8, half of it above
 #endif
 #ifndef ALLPOLE_FWD_S
 #define ALLPOLE_FWD_S 4  // ring stages per warp
 #endif
 #ifndef ALLPOLE_BWD_S
-#define ALLPOLE_BWD_S 3
+#define ALLPOLE_BWD_S 2
+#endif
+#ifndef ALLPOLE_FWD_MINB
+#define ALLPOLE_FWD_MINB 5  // CTAs per SM asked of the compiler (orders up to 8)
+#endif
+#ifndef ALLPOLE_BWD_MINB
+#define ALLPOLE_BWD_MINB 5
 #endif
 
 template <int NA, bool BWD, int VEC>
@@ -342,7 +350,8 @@ static int launch_allpole(const AllpoleArgs& a, cudaStream_t st) {
     constexpr int S = BWD ? ALLPOLE_BWD_S : ALLPOLE_FWD_S;
     constexpr int NTENS = BWD ? 2 : 1;
     constexpr size_t smem = (size_t)W * (7 * NA * NA * sizeof(double) + (size_t)S * NTENS * kStageF * sizeof(float));
-    auto kern = allpole_kernel<NA, BWD, VEC, W, S>;
+    constexpr int MINB = NA <= 8 ? (BWD ? ALLPOLE_BWD_MINB : ALLPOLE_FWD_MINB) : 1;
+    auto kern = allpole_kernel<NA, BWD, VEC, W, S, MINB>;
     static bool configured[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
