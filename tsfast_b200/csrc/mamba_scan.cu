@@ -222,8 +222,10 @@ __global__ void __launch_bounds__(DB* TPC) mamba_fwd_kernel(const MambaArgs p) {
             }
             return yp;
         };
-        auto emit = [&](int t, float y) {  // gated output of step t for this thread's channel
-            ob[t * DB + dl] = (y + Dp * st[kT * DB + t * DB + dl]) * st[2 * kT * DB + t * DB + dl];
+        // gated output of step t for this thread's channel (kept in a register until the tile is
+        // done: a shared-memory store inside the loop would pin every later load behind it)
+        auto gated = [&](int t, float y) -> float {
+            return (y + Dp * st[kT * DB + t * DB + dl]) * st[2 * kT * DB + t * DB + dl];
         };
         constexpr int G = (TPC >= 2 && TPC <= kT) ? TPC : 1;  // steps whose y sums are reduced together
         auto store_chk = [&](int t_done) {  // state after step t_done (tile-local) -> its checkpoint slot
@@ -242,6 +244,7 @@ __global__ void __launch_bounds__(DB* TPC) mamba_fwd_kernel(const MambaArgs p) {
             }
         };
         if (tlive == kT) {
+            float yout[kT / G];
 #pragma unroll
             for (int tg = 0; tg < kT; tg += G) {
                 float yv[G];
@@ -252,12 +255,16 @@ __global__ void __launch_bounds__(DB* TPC) mamba_fwd_kernel(const MambaArgs p) {
                 }
                 if constexpr (G > 1) {
                     group_reduce_scatter<G>(yv, ng);  // lane ng now owns step tg + ng
-                    emit(tg + ng, yv[0]);
+                    yout[tg / G] = gated(tg + ng, yv[0]);
                 } else {
 #pragma unroll
                     for (int off = 1; off < TPC; off <<= 1) yv[0] += __shfl_xor_sync(0xffffffffu, yv[0], off);
-                    if (ng == 0) emit(tg, yv[0]);
+                    yout[tg / G] = gated(tg, yv[0]);
                 }
+            }
+#pragma unroll
+            for (int j = 0; j < kT / G; ++j) {
+                if (G > 1 || ng == 0) ob[(j * G + (G > 1 ? ng : 0)) * DB + dl] = yout[j];
             }
         } else {
             for (int t = 0; t < tlive; ++t) {
@@ -265,7 +272,7 @@ __global__ void __launch_bounds__(DB* TPC) mamba_fwd_kernel(const MambaArgs p) {
                 if ((t + 1) % kTB == 0) store_chk(t);
 #pragma unroll
                 for (int off = 1; off < TPC; off <<= 1) yp += __shfl_xor_sync(0xffffffffu, yp, off);
-                if (ng == 0) emit(t, yp);
+                if (ng == 0) ob[t * DB + dl] = gated(t, yp);
             }
         }
     }
@@ -427,7 +434,8 @@ __global__ void __launch_bounds__(DB* TPC, 4) mamba_bwd_kernel(const MambaArgs p
         // one step of the reverse sweep for this thread's 4 states: updates G, grad_A, the
         // per-warp grad_B / grad_C rows, and returns this thread's shares of y, grad_delta and the
         // B-weighted sum that goes into grad_u
-        auto sweep_step = [&](int t, const float (&hv)[kNPT], float& yp, float& gdp, float& gus) {
+        constexpr int CNT = TPC >= 32 ? 8 : (TPC == 16 ? 4 : (TPC == 8 ? 2 : 1));  // row values a lane ends up owning
+        auto sweep_step = [&](int t, const float (&hv)[kNPT], float& yp, float& gdp, float& gus, float (&rv)[CNT]) {
             const float delta = st[t * DB + dl];
             const float uu = st[TD + t * DB + dl];
             const float gy = st[2 * TD + t * DB + dl];
@@ -456,46 +464,38 @@ __global__ void __launch_bounds__(DB* TPC, 4) mamba_bwd_kernel(const MambaArgs p
             if constexpr (TPC <= 4) rs_step<4, 2>(vals, lane);
             if constexpr (TPC <= 2) rs_step<2, 1>(vals, lane);
             if constexpr (TPC <= 1) rs_step<1, 1>(vals, lane);
-            constexpr int CNT = TPC >= 32 ? 8 : (TPC == 16 ? 4 : (TPC == 8 ? 2 : 1));
-            int base = 0;
-            if (TPC <= 16) base += (lane & 16) ? 4 : 0;
-            if (TPC <= 8) base += (lane & 8) ? 2 : 0;
-            if (TPC <= 4) base += (lane & 4) ? 1 : 0;
-            const bool writer = TPC > 2 || (TPC == 2 ? (lane & 2) == 0 : (lane & 3) == 0);
-            if (writer) {
-                float* r = red + (wid * kTB + t) * 2 * NPAD;
 #pragma unroll
-                for (int k = 0; k < CNT; ++k) {
-                    const int idx = base + k;
-                    r[(idx >> 2) * NPAD + n0 + (idx & 3)] = vals[k];
-                }
-            }
+            for (int k = 0; k < CNT; ++k) rv[k] = vals[k];
         };
         // finish the per-(t, d) gradients of step t from the channel-group sums
-        auto finish = [&](int t, float y_sum, float gd_sum, float gu_sum) {
+        auto finish = [&](int t, float y_sum, float gd_sum, float gu_sum, float (&o)[3]) {
             const float delta = st[t * DB + dl];
             const float uu = st[TD + t * DB + dl];
             const float gy = st[2 * TD + t * DB + dl];
-            obuf[t * DB + dl] = gd_sum * sigd[t * DB + dl];
-            obuf[TD + t * DB + dl] = fmaf(delta, gu_sum, gy * Dp);
-            obuf[2 * TD + t * DB + dl] = st[3 * TD + t * DB + dl] * fmaf(Dp, uu, y_sum);
+            o[0] = gd_sum * sigd[t * DB + dl];
+            o[1] = fmaf(delta, gu_sum, gy * Dp);
+            o[2] = st[3 * TD + t * DB + dl] * fmaf(Dp, uu, y_sum);
             gDp = fmaf(gy, uu, gDp);
         };
 
+        // Results stay in registers until the sweep is over: a shared-memory store inside the
+        // unrolled loop would keep the loads of later steps from being scheduled ahead of it.
+        float redv[kTB][CNT];      // this lane's grad_B / grad_C row values per step
+        float outv[kTB / G][3];    // gdraw, gu, gz of the steps this lane finishes
 #pragma unroll
         for (int tg = kTB - G; tg >= 0; tg -= G) {
             float yv[G], gdv[G], guv[G];
 #pragma unroll
             for (int k = G - 1; k >= 0; --k) {
                 yv[k] = 0.f, gdv[k] = 0.f, guv[k] = 0.f;
-                if (tg + k < tlive) sweep_step(tg + k, hreg[tg + k], yv[k], gdv[k], guv[k]);
+                if (tg + k < tlive) sweep_step(tg + k, hreg[tg + k], yv[k], gdv[k], guv[k], redv[tg + k]);
             }
             if (tg < tlive) {
                 if constexpr (G > 1) {
                     group_reduce_scatter<G>(yv, ng);  // lane ng now owns step tg + ng
                     group_reduce_scatter<G>(gdv, ng);
                     group_reduce_scatter<G>(guv, ng);
-                    if (tg + ng < tlive) finish(tg + ng, yv[0], gdv[0], guv[0]);
+                    if (tg + ng < tlive) finish(tg + ng, yv[0], gdv[0], guv[0], outv[tg / G]);
                 } else {
 #pragma unroll
                     for (int off = 1; off < TPC; off <<= 1) {
@@ -503,7 +503,34 @@ __global__ void __launch_bounds__(DB* TPC, 4) mamba_bwd_kernel(const MambaArgs p
                         gdv[0] += __shfl_xor_sync(0xffffffffu, gdv[0], off);
                         guv[0] += __shfl_xor_sync(0xffffffffu, guv[0], off);
                     }
-                    if (ng == 0) finish(tg, yv[0], gdv[0], guv[0]);
+                    if (ng == 0) finish(tg, yv[0], gdv[0], guv[0], outv[tg / G]);
+                }
+            }
+        }
+        {
+            int base = 0;  // index of the first row value this lane owns after the channel reduction
+            if (TPC <= 16) base += (lane & 16) ? 4 : 0;
+            if (TPC <= 8) base += (lane & 8) ? 2 : 0;
+            if (TPC <= 4) base += (lane & 4) ? 1 : 0;
+            const bool writer = TPC > 2 || (TPC == 2 ? (lane & 2) == 0 : (lane & 3) == 0);
+#pragma unroll
+            for (int t = 0; t < kTB; ++t) {
+                if (writer && t < tlive) {
+                    float* r = red + (wid * kTB + t) * 2 * NPAD;
+#pragma unroll
+                    for (int k = 0; k < CNT; ++k) {
+                        const int idx = base + k;
+                        r[(idx >> 2) * NPAD + n0 + (idx & 3)] = redv[t][k];
+                    }
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < kTB / G; ++j) {
+                const int t = j * G + (G > 1 ? ng : 0);
+                if ((G > 1 || ng == 0) && t < tlive) {
+                    obuf[t * DB + dl] = outv[j][0];
+                    obuf[TD + t * DB + dl] = outv[j][1];
+                    obuf[2 * TD + t * DB + dl] = outv[j][2];
                 }
             }
         }
