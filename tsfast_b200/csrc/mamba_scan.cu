@@ -245,13 +245,40 @@ __global__ void __launch_bounds__(DB* TPC) mamba_fwd_kernel(const MambaArgs p) {
         };
         if (tlive == kT) {
             float yout[kT / G];
+            float2 hp[2] = {make_float2(h[0], h[1]), make_float2(h[2], h[3])};
+            const float2 A2p[2] = {make_float2(A2[0], A2[1]), make_float2(A2[2], A2[3])};
 #pragma unroll
             for (int tg = 0; tg < kT; tg += G) {
+                // decays and injections of the whole group first (independent work: G x 4 exps in
+                // flight), then the short dependent chain through h
+                // (sm_100 packed arithmetic: one instruction per PAIR of states)
+                float2 lam[G][2], vin[G][2], cc[G][2];
+#pragma unroll
+                for (int k = 0; k < G; ++k) {
+                    const int t = tg + k;
+                    const float delta = st[t * DB + dl];
+                    const float du = delta * st[kT * DB + t * DB + dl];
+                    const float4 Bv = *reinterpret_cast<const float4*>(Bs + t * NPAD);
+                    const float4 Cv = *reinterpret_cast<const float4*>(Cs + t * NPAD);
+                    cc[k][0] = make_float2(Cv.x, Cv.y), cc[k][1] = make_float2(Cv.z, Cv.w);
+                    const float2 d2 = make_float2(delta, delta), du2 = make_float2(du, du);
+                    const float2 e0 = __fmul2_rn(d2, A2p[0]), e1 = __fmul2_rn(d2, A2p[1]);
+                    lam[k][0] = make_float2(ex2_fast(e0.x), ex2_fast(e0.y));
+                    lam[k][1] = make_float2(ex2_fast(e1.x), ex2_fast(e1.y));
+                    vin[k][0] = __fmul2_rn(du2, make_float2(Bv.x, Bv.y));
+                    vin[k][1] = __fmul2_rn(du2, make_float2(Bv.z, Bv.w));
+                }
                 float yv[G];
 #pragma unroll
                 for (int k = 0; k < G; ++k) {
-                    yv[k] = state_step(tg + k);
-                    if ((tg + k + 1) % kTB == 0) store_chk(tg + k);
+                    hp[0] = __ffma2_rn(lam[k][0], hp[0], vin[k][0]);
+                    hp[1] = __ffma2_rn(lam[k][1], hp[1], vin[k][1]);
+                    const float2 y2 = __ffma2_rn(hp[1], cc[k][1], __fmul2_rn(hp[0], cc[k][0]));
+                    yv[k] = y2.x + y2.y;
+                    if ((tg + k + 1) % kTB == 0) {
+                        h[0] = hp[0].x, h[1] = hp[0].y, h[2] = hp[1].x, h[3] = hp[1].y;
+                        store_chk(tg + k);
+                    }
                 }
                 if constexpr (G > 1) {
                     group_reduce_scatter<G>(yv, ng);  // lane ng now owns step tg + ng
@@ -262,6 +289,7 @@ __global__ void __launch_bounds__(DB* TPC) mamba_fwd_kernel(const MambaArgs p) {
                     yout[tg / G] = gated(tg, yv[0]);
                 }
             }
+            h[0] = hp[0].x, h[1] = hp[0].y, h[2] = hp[1].x, h[3] = hp[1].y;
 #pragma unroll
             for (int j = 0; j < kT / G; ++j) {
                 if (G > 1 || ng == 0) ob[(j * G + (G > 1 ? ng : 0)) * DB + dl] = yout[j];
