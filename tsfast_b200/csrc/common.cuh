@@ -59,9 +59,6 @@ struct alignas(sizeof(E) * V) Pack {
 // Streaming (evict-first) loads/stores: every sequence element crosses HBM once.
 template <typename P>
 __device__ __forceinline__ P ld_stream(const P* p) {
-#ifdef DIAG_EXP_PLAINLD
-    return *p;
-#endif
     P r;
     if constexpr (sizeof(P) == 4) {
         float t = __ldcs(reinterpret_cast<const float*>(p));
@@ -79,10 +76,7 @@ __device__ __forceinline__ P ld_stream(const P* p) {
 
 template <typename P>
 __device__ __forceinline__ void st_stream(P* p, const P& v) {
-#ifdef DIAG_EXP_PLAINLD
-    *p = v;
-    return;
-#endif
+
     if constexpr (sizeof(P) == 4) {
         float t;
         memcpy(&t, &v, 4);

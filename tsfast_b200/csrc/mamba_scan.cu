@@ -397,15 +397,23 @@ __global__ void __launch_bounds__(DB* TPC, 4) mamba_bwd_kernel(const MambaArgs p
         mcp_commit();
     }
 
-    float A1[kNPT], A2[kNPT], Gs[kNPT], gA[kNPT], lam_next[kNPT];
+    float2 A1p[2], A2p[2], Gp[2], gAp[2], lamn[2];  // states in pairs: (n0, n0+1), (n0+2, n0+3)
+    {
+        float A1[kNPT], G0[kNPT];
 #pragma unroll
-    for (int q = 0; q < kNPT; ++q) {
-        const bool ok = d_ok && (n0 + q) < N;
-        A1[q] = ok ? p.A[d * N + n0 + q] : 0.f;
-        A2[q] = A1[q] * kLog2e;
-        Gs[q] = (ok && p.ghlast != nullptr) ? p.ghlast[(b * D + d) * N + n0 + q] : 0.f;
-        gA[q] = 0.f;
-        lam_next[q] = 1.f;  // passes ghlast into G_{L-1} unchanged
+        for (int q = 0; q < kNPT; ++q) {
+            const bool ok = d_ok && (n0 + q) < N;
+            A1[q] = ok ? p.A[d * N + n0 + q] : 0.f;
+            G0[q] = (ok && p.ghlast != nullptr) ? p.ghlast[(b * D + d) * N + n0 + q] : 0.f;
+        }
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            A1p[k] = make_float2(A1[2 * k], A1[2 * k + 1]);
+            A2p[k] = make_float2(A1[2 * k] * kLog2e, A1[2 * k + 1] * kLog2e);
+            Gp[k] = make_float2(G0[2 * k], G0[2 * k + 1]);
+            gAp[k] = make_float2(0.f, 0.f);
+            lamn[k] = make_float2(1.f, 1.f);  // passes ghlast into G_{L-1} unchanged
+        }
     }
     const float Dp = d_ok ? p.Dp[d] : 0.f;
     float gDp = 0.f;
@@ -436,26 +444,28 @@ __global__ void __launch_bounds__(DB* TPC, 4) mamba_bwd_kernel(const MambaArgs p
         const float* Bs = st + 4 * TD + n0;
         const float* Cs = Bs + kTB * NPAD;
         // recompute the tile's states from its start state, kept in registers
-        float hreg[kTB][kNPT];
+        float2 hreg[kTB][2];
         {
             float h[kNPT];
             const float* ck = st + 4 * TD + 2 * kTB * NPAD + 4 * tid;
             const bool have = d_ok && (c > 0 || first_has_h0);
 #pragma unroll
             for (int q = 0; q < kNPT; ++q) h[q] = (have && n0 + q < N) ? ck[q] : 0.f;
+            float2 hp[2] = {make_float2(h[0], h[1]), make_float2(h[2], h[3])};
 #pragma unroll
             for (int t = 0; t < kTB; ++t) {
                 if (t < tlive) {
                     const float delta = st[t * DB + dl];
                     const float du = delta * st[TD + t * DB + dl];
                     const float4 Bv = *reinterpret_cast<const float4*>(Bs + t * NPAD);
-                    const float bq[kNPT] = {Bv.x, Bv.y, Bv.z, Bv.w};
-#pragma unroll
-                    for (int q = 0; q < kNPT; ++q)
-                        h[q] = fmaf(ex2_fast(delta * A2[q]), h[q], __fmul_rn(du, bq[q]));
+                    const float2 d2 = make_float2(delta, delta), du2 = make_float2(du, du);
+                    const float2 e0 = __fmul2_rn(d2, A2p[0]), e1 = __fmul2_rn(d2, A2p[1]);
+                    hp[0] = __ffma2_rn(make_float2(ex2_fast(e0.x), ex2_fast(e0.y)), hp[0],
+                                       __fmul2_rn(du2, make_float2(Bv.x, Bv.y)));
+                    hp[1] = __ffma2_rn(make_float2(ex2_fast(e1.x), ex2_fast(e1.y)), hp[1],
+                                       __fmul2_rn(du2, make_float2(Bv.z, Bv.w)));
                 }
-#pragma unroll
-                for (int q = 0; q < kNPT; ++q) hreg[t][q] = h[q];
+                hreg[t][0] = hp[0], hreg[t][1] = hp[1];
             }
         }
 
@@ -463,29 +473,41 @@ __global__ void __launch_bounds__(DB* TPC, 4) mamba_bwd_kernel(const MambaArgs p
         // per-warp grad_B / grad_C rows, and returns this thread's shares of y, grad_delta and the
         // B-weighted sum that goes into grad_u
         constexpr int CNT = TPC >= 32 ? 8 : (TPC == 16 ? 4 : (TPC == 8 ? 2 : 1));  // row values a lane ends up owning
-        auto sweep_step = [&](int t, const float (&hv)[kNPT], float& yp, float& gdp, float& gus, float (&rv)[CNT]) {
+        auto sweep_step = [&](int t, const float2 (&hv)[2], float& yp, float& gdp, float& gus, float (&rv)[CNT]) {
             const float delta = st[t * DB + dl];
             const float uu = st[TD + t * DB + dl];
             const float gy = st[2 * TD + t * DB + dl];
             const float du = delta * uu;
             const float4 Bv = *reinterpret_cast<const float4*>(Bs + t * NPAD);
             const float4 Cv = *reinterpret_cast<const float4*>(Cs + t * NPAD);
-            const float bq[kNPT] = {Bv.x, Bv.y, Bv.z, Bv.w}, cq[kNPT] = {Cv.x, Cv.y, Cv.z, Cv.w};
-            yp = 0.f, gdp = 0.f, gus = 0.f;
+            const float2 b2[2] = {make_float2(Bv.x, Bv.y), make_float2(Bv.z, Bv.w)};
+            const float2 c2[2] = {make_float2(Cv.x, Cv.y), make_float2(Cv.z, Cv.w)};
+            const float2 gy2 = make_float2(gy, gy), du2 = make_float2(du, du);
+            const float2 d2 = make_float2(delta, delta);
+            float2 y2 = make_float2(0.f, 0.f), gd2 = y2, gu2 = y2;
             float vals[8];
 #pragma unroll
-            for (int q = 0; q < kNPT; ++q) {
-                yp = fmaf(hv[q], cq[q], yp);
-                Gs[q] = fmaf(lam_next[q], Gs[q], gy * cq[q]);
+            for (int k = 0; k < 2; ++k) {  // one pass per PAIR of states (sm_100 packed arithmetic)
+                y2 = __ffma2_rn(hv[k], c2[k], y2);
+                Gp[k] = __ffma2_rn(lamn[k], Gp[k], __fmul2_rn(gy2, c2[k]));
                 // lam_t h_{t-1} = h_t - v_t, with v_t rounded exactly as in the recurrence (so 0 stays 0)
-                const float lhp = __fsub_rn(hv[q], __fmul_rn(du, bq[q]));
-                vals[q] = Gs[q] * du;       // grad_B contribution
-                vals[4 + q] = gy * hv[q];   // grad_C contribution
-                gA[q] = fmaf(Gs[q] * lhp, delta, gA[q]);
-                gdp = fmaf(Gs[q], fmaf(A1[q], lhp, uu * bq[q]), gdp);
-                gus = fmaf(Gs[q], bq[q], gus);
-                lam_next[q] = ex2_fast(delta * A2[q]);  // lam_t, the decay the step before will need
+                // (scalar on purpose: the packed multiply-then-add may be contracted into one fma)
+                const float2 lhp = make_float2(__fsub_rn(hv[k].x, __fmul_rn(du, b2[k].x)),
+                                               __fsub_rn(hv[k].y, __fmul_rn(du, b2[k].y)));
+                const float2 gb = __fmul2_rn(Gp[k], du2);   // grad_B contribution
+                const float2 gc = __fmul2_rn(gy2, hv[k]);   // grad_C contribution
+                vals[2 * k] = gb.x, vals[2 * k + 1] = gb.y;
+                vals[4 + 2 * k] = gc.x, vals[4 + 2 * k + 1] = gc.y;
+                const float2 P = __fmul2_rn(Gp[k], lhp);
+                gAp[k] = __ffma2_rn(P, d2, gAp[k]);
+                gd2 = __ffma2_rn(A1p[k], P, gd2);  // grad_delta = sum A (G lam h_prev) + u sum G B
+                gu2 = __ffma2_rn(Gp[k], b2[k], gu2);
+                const float2 e = __fmul2_rn(d2, A2p[k]);
+                lamn[k] = make_float2(ex2_fast(e.x), ex2_fast(e.y));  // lam_t, needed by the step before
             }
+            yp = y2.x + y2.y;
+            gus = gu2.x + gu2.y;
+            gdp = fmaf(uu, gus, gd2.x + gd2.y);
             // sum the 8 values over the channels of this warp; lanes end up owning distinct rows
             if constexpr (TPC <= 16) rs_step<16, 8>(vals, lane);
             if constexpr (TPC <= 8) rs_step<8, 4>(vals, lane);
@@ -608,8 +630,9 @@ __global__ void __launch_bounds__(DB* TPC, 4) mamba_bwd_kernel(const MambaArgs p
 #pragma unroll
         for (int q = 0; q < kNPT; ++q) {
             if (n0 + q < N) {
-                p.gA_part[(b * D + d) * N + n0 + q] = gA[q];
-                if (p.gh0 != nullptr) p.gh0[(b * D + d) * N + n0 + q] = lam_next[q] * Gs[q];
+                const float2 ga = gAp[q >> 1], gg = Gp[q >> 1], ll = lamn[q >> 1];
+                p.gA_part[(b * D + d) * N + n0 + q] = (q & 1) ? ga.y : ga.x;
+                if (p.gh0 != nullptr) p.gh0[(b * D + d) * N + n0 + q] = (q & 1) ? ll.y * gg.y : ll.x * gg.x;
             }
         }
         if (ng == 0) p.gDp_part[b * D + d] = gDp;
