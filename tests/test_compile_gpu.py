@@ -10,6 +10,8 @@ pytestmark = pytest.mark.gpu
 
 
 def _check(fn, args, grads_of):
+    for a in grads_of:
+        a.grad = None
     eager = fn(*args)
     eager.sum().backward()
     want = [a.grad.clone() for a in grads_of]
@@ -61,8 +63,8 @@ def test_non_contiguous_inputs_are_densified_inside_the_ops():
 
     torch.manual_seed(2)
     v = torch.randn(40, 3, 16, device="cuda").transpose(0, 1)  # [3, 40, 16], non-contiguous
-    lam = torch.rand(1, 16, device="cuda").expand(3, 16) * 0.9  # stride-0 batch axis
+    lam = (torch.rand(1, 16, device="cuda") * 0.9).expand(3, 16)  # stride-0 batch axis
     assert not v.is_contiguous() and not lam.is_contiguous()
     assert torch.equal(tb.diagonal_recurrence(lam, v), tb.diagonal_recurrence(lam.contiguous(), v.contiguous()))
-    a = torch.rand(40, 3, 16, device="cuda").transpose(0, 1) * 0.9
+    a = (torch.rand(40, 3, 16, device="cuda") * 0.9).transpose(0, 1)
     assert torch.equal(tb.selective_recurrence(a, v), tb.selective_recurrence(a.contiguous(), v.contiguous()))
