@@ -233,6 +233,7 @@ def run_gpu(args):
     e2e_ms = float("nan")
     if not args.kernel_only:
         e2e_ms = _e2e(args, torch, tsfast_b200, dev, a, b, g, barrier)
+    sys.stdout.flush()
 
     times = torch.tensor([ms, e2e_ms], device=dev)
     if world > 1:

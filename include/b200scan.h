@@ -122,6 +122,25 @@ int b200_mamba_bwd(int64_t B, int64_t L, int64_t D, int64_t N, const void* draw,
                    const void* gout, const void* ghlast, void* gdraw, void* gA, void* gBt, void* gCt, void* gu,
                    void* gz, void* gDp, void* gh0, void* workspace, size_t workspace_bytes, void* stream);
 
+/* ---- Mamba causal depthwise convolution + SiLU (the step that feeds S3) --------------------
+ * out[b,t,d] = silu(bias[d] + sum_{k<K} w[d,k] X(b, t-(K-1)+k, d)), X = cat(tail, x) along time.
+ * float32, 2 <= K <= 8.  x [B,L,D] with unit channel stride and the given element strides along
+ * batch and time (a chunk view of a wider projection is read in place); tail [B,D,K-1]; w [D,K];
+ * bias [D] or NULL; out [B,L,D] dense.  Replaces _conv_fwd / _conv_bwd and the eager tail-gradient
+ * code of tsfast/models/architectures/mamba/conv_triton.py:81-191,198-281 (ops
+ * tsfast::mamba_conv_silu(_bwd)); semantics of _causal_depthwise_silu, mamba/core.py:38-58.
+ * Backward: gy [B,L,D] dense; writes gx [B,L,D] dense, gtail [B,D,K-1], gw [D,K] and, when
+ * bias != NULL, gb [D]; weight/bias gradients go through per-(batch, segment) partials in the
+ * workspace, added in a fixed order. */
+int b200_conv_silu_fwd(int64_t B, int64_t L, int64_t D, int64_t K, const void* x, int64_t x_stride_b,
+                       int64_t x_stride_l, const void* tail, const void* w, const void* bias, void* out,
+                       void* stream);
+size_t b200_conv_silu_bwd_workspace_bytes(int64_t B, int64_t L, int64_t D, int64_t K);
+int b200_conv_silu_bwd(int64_t B, int64_t L, int64_t D, int64_t K, const void* gy, const void* x,
+                       int64_t x_stride_b, int64_t x_stride_l, const void* tail, const void* w,
+                       const void* bias, void* gx, void* gtail, void* gw, void* gb, void* workspace,
+                       size_t workspace_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -156,3 +156,25 @@ def allpole_bwd(g, a, y, y0=None):
     gy0 = np.empty_like(y0) if y0 is not None else None
     _call("allpole_bwd", _sfx(y), ((lanes, L, na), ()), (g, a, y, y0, ga, gw, gy0))
     return ga, gw, gy0
+
+
+# ------------------------------------------------------------------ Mamba causal conv + SiLU
+def conv_fwd(x, tail, w, bias=None):
+    """``silu(conv1d(cat(tail, x)))`` depthwise and causal: x [B,L,D], tail [B,D,K-1], w [D,K], bias [D]."""
+    x, tail, w, bias = _c(x), _c(tail), _c(w), _c(bias)
+    B, L, D = x.shape
+    K = w.shape[-1]
+    out = np.empty_like(x)
+    _call("conv_fwd", _sfx(x), ((B, L, D, K), ()), (x, tail, w, bias, out))
+    return out
+
+
+def conv_bwd(gy, x, tail, w, bias=None):
+    """Adjoint → ``(gx [B,L,D], gtail [B,D,K-1], gw [D,K], gb [D] | None)``."""
+    gy, x, tail, w, bias = _c(gy), _c(x), _c(tail), _c(w), _c(bias)
+    B, L, D = x.shape
+    K = w.shape[-1]
+    gx, gtail, gw = np.empty_like(x), np.empty_like(tail), np.empty_like(w)
+    gb = np.empty_like(bias) if bias is not None else None
+    _call("conv_bwd", _sfx(x), ((B, L, D, K), ()), (gy, x, tail, w, bias, gx, gtail, gw, gb))
+    return gx, gtail, gw, gb

@@ -429,3 +429,86 @@ void ORA(allpole_bwd)(int64_t lanes, int64_t L, int64_t na, const REAL* g, const
         }
     }
 }
+
+/* ------------------------------------------------------------------ Mamba causal depthwise conv + SiLU
+ * out[b,t,d] = silu(bias[d] + sum_k w[d,k] * X(b, t-(K-1)+k, d)), X(s) = x[b,s,d] for s >= 0 and
+ * tail[b,d,s+K-1] for s < 0 (the carried left context).  x/out [B,L,D] dense, tail [B,D,K-1],
+ * w [D,K], bias [D] or NULL.  Follows _causal_depthwise_silu of
+ * tsfast/models/architectures/mamba/core.py:38-58 (the eager definition the fused Triton kernel
+ * mamba/conv_triton.py:81-119 is tested against). */
+static inline REAL ORA(conv_x)(const REAL* x, const REAL* tail, int64_t b, int64_t s, int64_t d, int64_t L,
+                               int64_t D, int64_t K) {
+    return s >= 0 ? x[(b * L + s) * D + d] : tail[(b * D + d) * (K - 1) + s + K - 1];
+}
+
+void ORA(conv_fwd)(int64_t B, int64_t L, int64_t D, int64_t K, const REAL* x, const REAL* tail,
+                   const REAL* w, const REAL* bias, REAL* out) {
+#pragma omp parallel for collapse(2) schedule(static)
+    for (int64_t b = 0; b < B; ++b) {
+        for (int64_t t = 0; t < L; ++t) {
+            for (int64_t d = 0; d < D; ++d) {
+                REAL p = bias ? bias[d] : (REAL)0;
+                for (int64_t k = 0; k < K; ++k) p += w[d * K + k] * ORA(conv_x)(x, tail, b, t - (K - 1) + k, d, L, D, K);
+                out[(b * L + t) * D + d] = p * ORA(sigmoid)(p);
+            }
+        }
+    }
+}
+
+/* Adjoint (mamba/conv_triton.py:125-191,232-281): gpre = gy * sig(p) * (1 + p (1 - sig(p)));
+ * gx[b,s,d] = sum_k w[d,k] gpre[b, s+K-1-k, d]; gtail[b,d,j] = sum_k w[d,k] gpre[b, j-k, d];
+ * gw[d,k] = sum_{b,t} gpre[b,t,d] X(b, t-(K-1)+k, d); gb[d] = sum_{b,t} gpre (when bias != NULL). */
+void ORA(conv_bwd)(int64_t B, int64_t L, int64_t D, int64_t K, const REAL* gy, const REAL* x,
+                   const REAL* tail, const REAL* w, const REAL* bias, REAL* gx, REAL* gtail, REAL* gw,
+                   REAL* gb) {
+    REAL* gpre = (REAL*)malloc(sizeof(REAL) * (size_t)(B * L * D > 0 ? B * L * D : 1));
+#pragma omp parallel for collapse(2) schedule(static)
+    for (int64_t b = 0; b < B; ++b) {
+        for (int64_t t = 0; t < L; ++t) {
+            for (int64_t d = 0; d < D; ++d) {
+                REAL p = bias ? bias[d] : (REAL)0;
+                for (int64_t k = 0; k < K; ++k) p += w[d * K + k] * ORA(conv_x)(x, tail, b, t - (K - 1) + k, d, L, D, K);
+                const REAL sg = ORA(sigmoid)(p);
+                gpre[(b * L + t) * D + d] = gy[(b * L + t) * D + d] * sg * ((REAL)1 + p * ((REAL)1 - sg));
+            }
+        }
+    }
+#pragma omp parallel for collapse(2) schedule(static)
+    for (int64_t b = 0; b < B; ++b) {
+        for (int64_t s = 0; s < L; ++s) {
+            for (int64_t d = 0; d < D; ++d) {
+                REAL v = 0;
+                for (int64_t k = 0; k < K; ++k) {
+                    const int64_t t = s + K - 1 - k;
+                    if (t < L) v += w[d * K + k] * gpre[(b * L + t) * D + d];
+                }
+                gx[(b * L + s) * D + d] = v;
+            }
+        }
+    }
+    for (int64_t b = 0; b < B; ++b)
+        for (int64_t d = 0; d < D; ++d)
+            for (int64_t j = 0; j < K - 1; ++j) {
+                REAL v = 0;
+                for (int64_t k = 0; k <= j; ++k)
+                    if (j - k < L) v += w[d * K + k] * gpre[(b * L + (j - k)) * D + d];
+                gtail[(b * D + d) * (K - 1) + j] = v;
+            }
+#pragma omp parallel for schedule(static)
+    for (int64_t d = 0; d < D; ++d) {
+        REAL sb = 0;
+        for (int64_t k = 0; k < K; ++k) {
+            REAL sw = 0;
+            for (int64_t b = 0; b < B; ++b)
+                for (int64_t t = 0; t < L; ++t)
+                    sw += gpre[(b * L + t) * D + d] * ORA(conv_x)(x, tail, b, t - (K - 1) + k, d, L, D, K);
+            gw[d * K + k] = sw;
+        }
+        if (gb) {
+            for (int64_t b = 0; b < B; ++b)
+                for (int64_t t = 0; t < L; ++t) sb += gpre[(b * L + t) * D + d];
+            gb[d] = sb;
+        }
+    }
+    free(gpre);
+}

@@ -279,9 +279,39 @@ def make_lru():
     print("deeplru", len(store), "arrays")
 
 
+# ------------------------------------------------------------------ Mamba causal conv + SiLU
+def make_conv():
+    """The eager conv section of MambaLayer (mamba/core.py:38-58) in float64, gradients by autograd."""
+    from tsfast.models.architectures.mamba.core import _causal_depthwise_silu
+
+    cases = [(2, 19, 20, 4, True), (2, 3, 8, 4, True), (1, 1, 5, 2, False), (3, 70, 33, 8, True), (2, 40, 16, 3, False)]
+    store, names = {}, []
+    for idx, (Bsz, L, D, K, with_bias) in enumerate(cases):
+        gen = torch.Generator().manual_seed(5000 + idx)
+        rn = lambda *s: torch.randn(*s, generator=gen)  # noqa: E731
+        x, tail, w = rn(Bsz, L, D), rn(Bsz, D, K - 1), rn(D, 1, K) * 0.5
+        bias = rn(D) if with_bias else None
+        gy = rn(Bsz, L, D)
+        name = f"case{idx}"
+        names.append(name)
+        leaves = [_leaf(_to64(t)) for t in (x, tail, w)]
+        b_ = _leaf(_to64(bias))
+        y = _causal_depthwise_silu(leaves[0], leaves[1], leaves[2], b_ if b_ is not None else torch.zeros(D, dtype=torch.float64))
+        y.backward(_to64(gy))
+        store.update({f"{name}_x": _np(x), f"{name}_tail": _np(tail), f"{name}_w": _np(w[:, 0]), f"{name}_gy": _np(gy),
+                      f"{name}_ref64_out": _np(y), f"{name}_ref64_gx": _np(leaves[0].grad),
+                      f"{name}_ref64_gtail": _np(leaves[1].grad), f"{name}_ref64_gw": _np(leaves[2].grad[:, 0])})
+        if with_bias:
+            store[f"{name}_bias"] = _np(bias)
+            store[f"{name}_ref64_gb"] = _np(b_.grad)
+    store["names"] = np.array(names)
+    np.savez_compressed(HERE / "conv.npz", **store)
+    print("conv", len(names), "cases")
+
+
 if __name__ == "__main__":
     torch.set_num_threads(4)
-    which = sys.argv[1:] or ["diag", "sel", "mamba", "allpole", "lru"]
+    which = sys.argv[1:] or ["diag", "sel", "mamba", "allpole", "lru", "conv"]
     if "diag" in which:
         make_diag("diag")
     if "sel" in which:
@@ -292,3 +322,5 @@ if __name__ == "__main__":
         make_allpole()
     if "lru" in which:
         make_lru()
+    if "conv" in which:
+        make_conv()

@@ -79,6 +79,21 @@ def test_allpole(oracle, f64):
             assert rel_err(gy0, c.ref64_gy0) < tol, (c.name, "gy0")
 
 
+@pytest.mark.parametrize("f64", [True, False])
+def test_conv(oracle, f64):
+    tol = TOL64 if f64 else TOL32
+    for c in load_golden("conv"):
+        x, tail, w, bias, gy = (_cast(t, f64) for t in (c.x, c.tail, c.w, c.bias, c.gy))
+        out = oracle.conv_fwd(x, tail, w, bias)
+        assert rel_err(out, c.ref64_out) < tol, (c.name, "out")
+        gx, gtail, gw, gb = oracle.conv_bwd(gy, x, tail, w, bias)
+        assert rel_err(gx, c.ref64_gx) < tol, (c.name, "gx")
+        assert rel_err(gtail, c.ref64_gtail) < tol, (c.name, "gtail")
+        assert rel_err(gw, c.ref64_gw) < tol, (c.name, "gw")
+        if bias is not None:
+            assert rel_err(gb, c.ref64_gb) < tol, (c.name, "gb")
+
+
 def test_allpole_unstable_pole_overflows_without_crash(oracle):
     """An unstable filter must run to non-finite values, not fault (reference tests/test_dynonet.py:165-174)."""
     a = np.array([[-3.0]], dtype=np.float32)
