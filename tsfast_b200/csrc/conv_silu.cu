@@ -225,14 +225,25 @@ __global__ void __launch_bounds__(kConvThreads) conv_silu_bwd_kernel(const ConvA
     }
 }
 
-// out[i] = sum_k in[k * stride + i], k ascending (fixed order)
-__global__ void conv_sum_leading_kernel(const float* __restrict__ in, float* __restrict__ out, long long count,
-                                        long long stride, int Kp) {
-    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= count) return;
+// out[i] = sum_k in[k * stride + i] for many partials: 8 threads per output each add every 8th
+// partial in ascending order, then the 8 sub-sums are added in lane order (a fixed order, so the
+// result is reproducible); 32 outputs per block keep the reads of one partial coalesced.
+__global__ void __launch_bounds__(256) conv_sum_parts_kernel(const float* __restrict__ in, float* __restrict__ out,
+                                                             long long count, long long stride, int parts) {
+    __shared__ float sh[8][33];
+    const int o = threadIdx.x & 31, pl = threadIdx.x >> 5;
+    const long long i = (long long)blockIdx.x * 32 + o;
     float s = 0.f;
-    for (int k = 0; k < Kp; ++k) s += in[k * stride + i];
-    out[i] = s;
+    if (i < count)
+        for (int k = pl; k < parts; k += 8) s += in[k * stride + i];
+    sh[pl][o] = s;
+    __syncthreads();
+    if (pl == 0 && i < count) {
+        float t = 0.f;
+#pragma unroll
+        for (int q = 0; q < 8; ++q) t += sh[q][o];
+        out[i] = t;
+    }
 }
 
 template <int K, int VEC>
@@ -331,8 +342,8 @@ int b200_conv_silu_bwd(int64_t B, int64_t L, int64_t D, int64_t K, const void* g
                  : dispatch_conv_k<1>((int)K, true, bias != nullptr, a, st);
     if (rc != B200_OK) return rc;
     const long long cw = D * K;
-    conv_sum_leading_kernel<<<(unsigned int)((cw + 255) / 256), 256, 0, st>>>(a.gw_part, (float*)gw, cw, cw, (int)parts);
-    if (bias) conv_sum_leading_kernel<<<(unsigned int)((D + 255) / 256), 256, 0, st>>>(a.gb_part, (float*)gb, D, D, (int)parts);
+    conv_sum_parts_kernel<<<(unsigned int)((cw + 31) / 32), 256, 0, st>>>(a.gw_part, (float*)gw, cw, cw, (int)parts);
+    if (bias) conv_sum_parts_kernel<<<(unsigned int)((D + 31) / 32), 256, 0, st>>>(a.gb_part, (float*)gb, D, D, (int)parts);
     return cudaGetLastError() == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
 }
 
