@@ -42,6 +42,19 @@ METRIC = "scan GB/s (fwd+bwd)"
 WORKLOAD = "C2: time-varying diagonal scan fwd+bwd, B=64 T=4096 D=256 fp32 per GPU, h0=0"
 
 
+def _emit(line: dict) -> None:
+    """Print the result as the LAST line of stdout: libraries that write through C stdio (NCCL's
+    version banner) are flushed first, so nothing buffered can land after the JSON line."""
+    import ctypes
+
+    sys.stdout.flush()
+    try:
+        ctypes.CDLL(None).fflush(None)
+    except OSError:
+        pass
+    print(json.dumps(line), flush=True)
+
+
 def _peaks():
     """Measured HBM peak of this pool's B200s, else the stated fallback."""
     f = ROOT / "MEASURED_PEAKS.json"
@@ -162,7 +175,7 @@ def run_reference(args):
         "e2e": {"value": base["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line))
+    _emit(line)
 
 
 # ----------------------------------------------------------------------------- GPU arm
@@ -328,7 +341,7 @@ def _report(args, world, rank, ms, e2e_ms, fwd_ms, bwd_ms, clock_rec):
         # dram__bytes_read.sum + dram__bytes_write.sum of one adjoint launch at this workload, from the
         # ncu capture summarised in profiles/sel_scan_c2_ncu_full.md
         line["roofline"]["traffic"] = ADJOINT_DRAM_TRAFFIC_BYTES
-        print(json.dumps(line))
+        _emit(line)
 
 
 # ----------------------------------------------------------------------------- other workloads
@@ -525,7 +538,7 @@ def run_workload(args):
                     "kind": "port", "sample": f"{rows} of {wl['rows']} batch rows, fwd+bwd, median of {cnt} passes of "
                     f"{sec * 1e3:.1f} ms; float32 C port of the reference's CPU algorithm, OpenMP"}
         bwd_gbs, fwd_gbs = wl["bwd_bytes"] / bwd_ms / 1e6, wl["fwd_bytes"] / fwd_ms / 1e6
-        print(json.dumps({
+        _emit({
             "metric": METRIC, "value": round(step_bytes * world / ms / 1e6, 1), "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": wl["dtype"], "data": "synthetic",
@@ -543,7 +556,7 @@ def run_workload(args):
             "e2e": None if args.kernel_only else {"value": round(step_bytes * world / e2e_ms / 1e6, 2), "unit": "GB/s",
                                                   "h2d_bytes_per_step": wl["h2d"], "d2h_bytes_per_step": wl["d2h"],
                                                   "ms_per_step": round(e2e_ms, 3)},
-            "gpu_launches": wl["launches"] * args.steps, "clocks": clock_rec}))
+            "gpu_launches": wl["launches"] * args.steps, "clocks": clock_rec})
     if world > 1:
         dist.destroy_process_group()
 
@@ -655,7 +668,7 @@ def _run_c5(args, torch, dist, dev, world, rank, local):
         E = Bn * T * ds * 8
         scan_bytes = nl * 5 * E
         bwd_gbs, fwd_gbs = 3 * E / bwd_ms / 1e6, 2 * E / fwd_ms / 1e6
-        print(json.dumps({
+        _emit({
             "metric": METRIC, "value": round(scan_bytes * world / ms / 1e6, 1), "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 3), "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "c64", "data": "synthetic",
@@ -675,7 +688,7 @@ def _run_c5(args, torch, dist, dev, world, rank, local):
             "cpu_baseline": None,
             "e2e": {"value": round(scan_bytes * world / e2e_ms / 1e6, 2), "unit": "GB/s",
                     "h2d_bytes_per_step": 2 * Bn * T * 4, "d2h_bytes_per_step": 4, "ms_per_step": round(e2e_ms, 3)},
-            "gpu_launches": 2 * nl * args.steps, "clocks": clock_rec}))
+            "gpu_launches": 2 * nl * args.steps, "clocks": clock_rec})
     if world > 1:
         dist.destroy_process_group()
 
