@@ -656,7 +656,11 @@ __global__ void sum_leading_kernel(const float* __restrict__ in, float* __restri
 #ifndef MAMBA_BWD_S
 #define MAMBA_BWD_S 3  // ring stages of the adjoint
 #endif
-constexpr int kMambaThreads = 128;
+#ifndef MAMBA_THREADS
+#define MAMBA_THREADS 128  // threads per CTA (fewer when the state dimension is small enough)
+#endif
+// channels per CTA: MAMBA_THREADS / TPC, at least 4 so that rows stay 16-byte copyable
+constexpr int mamba_db(int tpc) { return MAMBA_THREADS / tpc > 4 ? MAMBA_THREADS / tpc : 4; }
 
 static int tpc_for(long long N) {  // threads per channel: 4 states each, power of two
     int t = 1;
@@ -678,7 +682,7 @@ static int set_smem(K kern, size_t bytes, bool* configured) {
 
 template <int TPC, bool STORE_CHK, int VEC>
 static int launch_mamba_fwd(const MambaArgs& a, cudaStream_t st) {
-    constexpr int DB = kMambaThreads / TPC, S = MAMBA_FWD_S;
+    constexpr int DB = mamba_db(TPC), S = MAMBA_FWD_S, NTHR = DB * TPC;
     constexpr size_t smem = sizeof(float) * ((size_t)S * (3 * kT * DB + 2 * kT * kNPT * TPC) + 2 * kT * DB);
     auto kern = mamba_fwd_kernel<TPC, DB, STORE_CHK, VEC, S>;
     static bool configured[64] = {false};
@@ -687,21 +691,21 @@ static int launch_mamba_fwd(const MambaArgs& a, cudaStream_t st) {
     p.ndb = (a.D + DB - 1) / DB;
     const long long grid = a.B * p.ndb;
     if (grid > 0x7fffffffLL) return B200_ERR_UNSUPPORTED;
-    kern<<<(unsigned int)grid, kMambaThreads, smem, st>>>(p);
+    kern<<<(unsigned int)grid, NTHR, smem, st>>>(p);
     return cudaGetLastError() == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
 }
 
 template <int TPC, int VEC>
 static int launch_mamba_bwd(const MambaArgs& a, cudaStream_t st) {
-    constexpr int DB = kMambaThreads / TPC, S = MAMBA_BWD_S, NPAD = kNPT * TPC, NW = kMambaThreads / 32;
-    constexpr size_t smem = sizeof(float) * ((size_t)S * (4 * kTB * DB + 2 * kTB * NPAD + 4 * kMambaThreads) +
+    constexpr int DB = mamba_db(TPC), S = MAMBA_BWD_S, NPAD = kNPT * TPC, NTHR = DB * TPC, NW = NTHR / 32;
+    constexpr size_t smem = sizeof(float) * ((size_t)S * (4 * kTB * DB + 2 * kTB * NPAD + 4 * NTHR) +
                                              4 * kTB * DB + NW * kTB * 2 * NPAD);
     auto kern = mamba_bwd_kernel<TPC, DB, VEC, S>;
     static bool configured[64] = {false};
     if (set_smem(kern, smem, configured) != B200_OK) return B200_ERR_LAUNCH;
     const long long grid = a.B * a.ndb;
     if (grid > 0x7fffffffLL) return B200_ERR_UNSUPPORTED;
-    kern<<<(unsigned int)grid, kMambaThreads, smem, st>>>(a);
+    kern<<<(unsigned int)grid, NTHR, smem, st>>>(a);
     return cudaGetLastError() == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
 }
 
@@ -755,7 +759,7 @@ struct MambaWs {
 
 static MambaWs mamba_ws(long long B, long long L, long long D, long long N) {
     MambaWs w;
-    const int DB = kMambaThreads / tpc_for(N);
+    const int DB = mamba_db(tpc_for(N));
     w.ndb = (D + DB - 1) / DB;
     size_t off = 0;
     w.off_gA = off;
