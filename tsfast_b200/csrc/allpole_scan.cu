@@ -4,15 +4,17 @@
 // Data layout: w, y, g [lanes, L] with TIME contiguous per lane; a, y0 [lanes, na]; the carried
 // state is s[j] = y_{t-1-j} (newest first), which is also the layout of y0.
 //
-// One warp owns one lane and walks its sequence in tiles of 512 steps, 16 consecutive steps per
-// thread.  The recurrence is linear in (state, input), so a 16-step segment maps its start state
-// to its end state as s' = M s + r with M = (companion matrix)^16 the same for every segment and
-// r the segment's zero-state response.  Per tile:
-//   1. each thread runs its 16 steps from a zero state (registers) to get r,
+// One warp owns one lane and walks its sequence in tiles of 32*SEG steps, SEG = 32 consecutive
+// steps per thread.  The recurrence is linear in (state, input), so a SEG-step segment maps its
+// start state to its end state as s' = M s + r with M = (companion matrix)^SEG the same for every
+// segment and r the segment's zero-state response.  Per tile:
+//   1. each thread runs its SEG steps from a zero state (registers) to get r,
 //   2. a warp-shuffle Kogge-Stone scan over the 32 segments composes the affine maps; step d
 //      uses M^(2^d), and the carry from the previous tile enters through thread 0,
-//   3. each thread re-runs its 16 steps from its true start state and the tile is stored.
-// The five powers M^(1,2,4,8,16) are built once per lane at kernel start by repeated squaring and
+//   3. each thread re-runs its SEG steps from its true start state and the tile is stored.
+// (Longer segments spread the cost of step 2 over more elements: SEG = 32 took the forward from
+// 4.4 to 6.2 TB/s on B200.)
+// The five powers M^(1,2,4,8,16) (in units of one segment) are built once per lane at kernel start by repeated squaring and
 // kept in shared memory.  Powers and the composition of segment states are float64: with poles
 // near the unit circle M has large entries that cancel, and a float32 composition loses ten times
 // the accuracy of the sequential float32 loop, while float64 matches it (steps 1 and 3, i.e. all
@@ -21,11 +23,13 @@
 //
 // Memory pipeline: every warp keeps S-1 tiles in flight in a private shared-memory ring filled by
 // coalesced 16-byte cp.async (4-byte when L or a pointer is not 16-byte aligned); chunks are
-// padded to 80 bytes so that the per-thread 64-byte reads are bank-conflict free.  Results go
+// padded by 16 bytes so that the per-thread 16-byte reads are bank-conflict free.  Results go
 // back through the same buffer and leave as coalesced 16-byte stores.  No workspace, no atomics:
 // the adjoint's grad_a is accumulated per thread in registers across all tiles and reduced with
 // a fixed butterfly at the end, so results are bitwise reproducible.
 #include <float.h>
+
+#include <type_traits>
 
 #include "common.cuh"
 
@@ -42,10 +46,8 @@ struct AllpoleArgs {
     long long lanes, L;
 };
 
-constexpr int kSeg = 16;            // steps per thread
-constexpr int kTile = 32 * kSeg;    // steps per warp tile
-constexpr int kChunk = kSeg + 4;    // floats per thread chunk in shared memory (80 bytes)
-constexpr int kStageF = 32 * kChunk;  // floats per staged tensor tile
+// Steps per thread (SEG, a template parameter: 16 or 32), hence 32*SEG steps per warp tile; a
+// thread's chunk is padded by 4 floats in shared memory so that 16-byte reads are conflict free.
 
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
     const unsigned int d = static_cast<unsigned int>(__cvta_generic_to_shared(smem_dst));
@@ -80,9 +82,11 @@ __device__ __forceinline__ float iir_step(const float (&a)[NA], float (&s)[NA], 
     return y;
 }
 
-template <int NA, bool BWD, int VEC, int W, int S, int MINB>
+template <int NA, bool BWD, int VEC, int W, int S, int MINB, int SEG>
 __global__ void __launch_bounds__(32 * W, MINB) allpole_kernel(const AllpoleArgs p) {
     static_assert(VEC == 4 || VEC == 1, "pieces are 16 or 4 bytes");
+    static_assert(SEG >= NA && SEG % 4 == 0, "a segment must hold the whole state");
+    constexpr int kSeg = SEG, kTile = 32 * SEG, kChunk = SEG + 4, kStageF = 32 * kChunk;
     constexpr int NTENS = BWD ? 2 : 1;
     constexpr int PIECES = kTile / VEC;  // copy pieces per tile and tensor
     constexpr int PPC = kSeg / VEC;      // pieces per thread chunk
@@ -93,9 +97,12 @@ __global__ void __launch_bounds__(32 * W, MINB) allpole_kernel(const AllpoleArgs
     const long long lane = (long long)blockIdx.x * W + w;
     if (lane >= p.lanes) return;  // warps never synchronise with each other
 
-    double* Md = reinterpret_cast<double*>(smem_raw) + w * (7 * NA * NA);  // squaring scratch (2 matrices)
-    double* Mp = Md + 2 * NA * NA;                                           // M^(2^d), d = 0..4
-    float* ring = reinterpret_cast<float*>(reinterpret_cast<double*>(smem_raw) + W * (7 * NA * NA)) +
+    // 7 matrices of doubles per warp, rounded up to an even count so that the float ring behind
+    // them stays 16-byte aligned for every order and warp count
+    constexpr int MDW = (7 * NA * NA + 1) & ~1;
+    double* Md = reinterpret_cast<double*>(smem_raw) + w * MDW;  // squaring scratch (2 matrices)
+    double* Mp = Md + 2 * NA * NA;                                // M^(2^d), d = 0..4
+    float* ring = reinterpret_cast<float*>(reinterpret_cast<double*>(smem_raw) + W * MDW) +
                   w * (S * NTENS * kStageF);  // [S][NTENS][32][kChunk]
 
     const long long L = p.L;
@@ -198,7 +205,8 @@ __global__ void __launch_bounds__(32 * W, MINB) allpole_kernel(const AllpoleArgs
                 yv[4 * q] = u4.x, yv[4 * q + 1] = u4.y, yv[4 * q + 2] = u4.z, yv[4 * q + 3] = u4.w;
             }
         }
-        if (ph < 0 || ph + kTile > L) {  // edge tile only: steps outside the sequence get zero input
+        const bool edge = ph < 0 || ph + kTile > L;
+        if (edge) {  // edge tile only: steps outside the sequence get zero input
 #pragma unroll
             for (int r = 0; r < kSeg; ++r) {
                 const bool okr = (tbase + r) >= 0 && (tbase + r) < L;
@@ -257,15 +265,27 @@ __global__ void __launch_bounds__(32 * W, MINB) allpole_kernel(const AllpoleArgs
 #pragma unroll
         for (int j = 0; j < NA; ++j) cin[j] = __shfl_sync(0xffffffffu, sd[j], 31);
 
-        // 3. the true run of this segment
+        // 3. the true run of this segment (interior tiles take the copy without range checks)
+        auto true_run = [&](auto edge_tag) {
+            constexpr bool EDGE = decltype(edge_tag)::value;
 #pragma unroll
-        for (int k = 0; k < kSeg; ++k) {
-            const int r = BWD ? kSeg - 1 - k : k;
-            if constexpr (BWD) {  // grad_a_k += G_{t+1+k} * y_t with the state BEFORE the step
+            for (int k = 0; k < kSeg; ++k) {
+                const int r = BWD ? kSeg - 1 - k : k;
+                if constexpr (BWD) {  // grad_a_k += G_{t+1+k} * y_t with the state BEFORE the step
+                    // (steps past the sequence are skipped: an unstable filter may have run its
+                    // state to inf there, and inf * 0 must not reach the sum)
+                    if (!EDGE || ((tbase + r) >= 0 && (tbase + r) < L)) {
 #pragma unroll
-                for (int j = 0; j < NA; ++j) acc_a[j] = fmaf(st[j], yv[r], acc_a[j]);
+                        for (int j = 0; j < NA; ++j) acc_a[j] = fmaf(st[j], yv[r], acc_a[j]);
+                    }
+                }
+                v[r] = iir_step<NA>(a, st, v[r]);
             }
-            v[r] = iir_step<NA>(a, st, v[r]);
+        };
+        if (edge) {
+            true_run(std::true_type{});
+        } else {
+            true_run(std::false_type{});
         }
 
         // stage the results in this thread's chunk and store the tile coalesced
@@ -328,30 +348,42 @@ __global__ void __launch_bounds__(32 * W, MINB) allpole_kernel(const AllpoleArgs
 }
 
 // ------------------------------------------------------------------------------- host side
-#ifndef ALLPOLE_W
-#define ALLPOLE_W 4  // lanes (warps) per CTA for orders up to 8, half of it above
+#ifndef ALLPOLE_FWD_W
+#define ALLPOLE_FWD_W 2  // lanes (warps) per CTA for orders up to 8, half of it above
+#endif
+#ifndef ALLPOLE_BWD_W
+#define ALLPOLE_BWD_W 2
 #endif
 #ifndef ALLPOLE_FWD_S
-#define ALLPOLE_FWD_S 4  // ring stages per warp
+#define ALLPOLE_FWD_S 2  // ring stages per warp
 #endif
 #ifndef ALLPOLE_BWD_S
-#define ALLPOLE_BWD_S 2
+#define ALLPOLE_BWD_S 3
 #endif
 #ifndef ALLPOLE_FWD_MINB
-#define ALLPOLE_FWD_MINB 5  // CTAs per SM asked of the compiler (orders up to 8)
+#define ALLPOLE_FWD_MINB 8  // CTAs per SM asked of the compiler (orders up to 8)
 #endif
 #ifndef ALLPOLE_BWD_MINB
-#define ALLPOLE_BWD_MINB 5
+#define ALLPOLE_BWD_MINB 6
+#endif
+#ifndef ALLPOLE_FWD_SEG
+#define ALLPOLE_FWD_SEG 32  // steps per thread, forward
+#endif
+#ifndef ALLPOLE_BWD_SEG
+#define ALLPOLE_BWD_SEG 32  // steps per thread, adjoint
 #endif
 
 template <int NA, bool BWD, int VEC>
 static int launch_allpole(const AllpoleArgs& a, cudaStream_t st) {
-    constexpr int W = NA <= 8 ? ALLPOLE_W : ALLPOLE_W / 2;  // high orders: the matrix powers take the shared memory
+    constexpr int W0 = BWD ? ALLPOLE_BWD_W : ALLPOLE_FWD_W;
+    constexpr int W = (NA <= 8 || W0 == 1) ? W0 : W0 / 2;  // high orders: the matrix powers take the shared memory
     constexpr int S = BWD ? ALLPOLE_BWD_S : ALLPOLE_FWD_S;
     constexpr int NTENS = BWD ? 2 : 1;
-    constexpr size_t smem = (size_t)W * (7 * NA * NA * sizeof(double) + (size_t)S * NTENS * kStageF * sizeof(float));
+    constexpr int SEG = BWD ? ALLPOLE_BWD_SEG : ALLPOLE_FWD_SEG;
+    constexpr size_t smem =
+        (size_t)W * (((7 * NA * NA + 1) & ~1) * sizeof(double) + (size_t)S * NTENS * 32 * (SEG + 4) * sizeof(float));
     constexpr int MINB = NA <= 8 ? (BWD ? ALLPOLE_BWD_MINB : ALLPOLE_FWD_MINB) : 1;
-    auto kern = allpole_kernel<NA, BWD, VEC, W, S, MINB>;
+    auto kern = allpole_kernel<NA, BWD, VEC, W, S, MINB, SEG>;
     static bool configured[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
