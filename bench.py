@@ -37,6 +37,7 @@ FWD_BYTES = 3 * TENSOR_BYTES  # a, b -> h
 BWD_BYTES = 5 * TENSOR_BYTES  # g, a, h -> ga, gb
 STEP_BYTES = FWD_BYTES + BWD_BYTES
 E2E_CHUNKS = 8  # batch slices the end-to-end step is pipelined over
+E2E_STREAMS = 3  # streams the slices are issued on, round-robin
 ADJOINT_DRAM_TRAFFIC_BYTES = 805_204_224 + 495_119_360
 METRIC = "scan GB/s (fwd+bwd)"
 WORKLOAD = "C2: time-varying diagonal scan fwd+bwd, B=64 T=4096 D=256 fp32 per GPU, h0=0"
@@ -261,13 +262,13 @@ def _e2e(args, torch, tsfast_b200, dev, a, b, g, barrier):
     """Same step through the public API from pinned host buffers, copies inside the timed region.
 
     The sequences of a batch are independent, so the step is issued as E2E_CHUNKS batch slices
-    round-robin on three streams: the host-to-device copy of one slice, the scans of another and
+    round-robin on E2E_STREAMS streams: the host-to-device copy of one slice, the scans of another and
     the device-to-host copy of a third overlap, which keeps both PCIe directions busy.  Every
     byte of a, b, g goes in and every byte of h, ga, gb comes back each step.
     """
     ha, hb, hg = (torch.empty(B, T, D, pin_memory=True).copy_(t) for t in (a, b, g))
     ho, hga, hgb = (torch.empty(B, T, D, pin_memory=True) for _ in range(3))
-    streams = [torch.cuda.Stream(device=dev) for _ in range(3)]
+    streams = [torch.cuda.Stream(device=dev) for _ in range(E2E_STREAMS)]
     rows = B // E2E_CHUNKS
 
     def e2e_step():
@@ -334,7 +335,7 @@ def _report(args, world, rank, ms, e2e_ms, fwd_ms, bwd_ms, clock_rec):
                 "value": round(STEP_BYTES * world / (e2e_ms * 1e-3) / 1e9, 2), "unit": "GB/s",
                 "h2d_bytes_per_step": 3 * TENSOR_BYTES, "d2h_bytes_per_step": 3 * TENSOR_BYTES,
                 "ms_per_step": round(e2e_ms, 3),
-                "how": f"{E2E_CHUNKS} batch slices round-robin on 3 streams (copies overlap the scans and each other)"},
+                "how": f"{E2E_CHUNKS} batch slices round-robin on {E2E_STREAMS} streams (copies overlap the scans and each other)"},
             "gpu_launches": 2 * args.steps,  # device-resident region; the end-to-end region launches 2 per slice
             "clocks": clock_rec,
         }

@@ -864,12 +864,42 @@ static int launch(const DiagArgs& a, const DiagPlan& pl, cudaStream_t st) {
 #define STRM_BWD_MINB 3
 #endif
 
+// complex64 streams 8-byte elements and is best with other shapes (measured at M=128, L=2000,
+// N=256: adjoint 5.1 -> 6.3 TB/s, forward 5.6 -> 5.8 TB/s against the float32 shapes)
+#ifndef STRM_C_FWD_BYTES
+#define STRM_C_FWD_BYTES 64
+#endif
+#ifndef STRM_C_BWD_BYTES
+#define STRM_C_BWD_BYTES 128
+#endif
+#ifndef STRM_C_FWD_W
+#define STRM_C_FWD_W 8
+#endif
+#ifndef STRM_C_BWD_W
+#define STRM_C_BWD_W 4
+#endif
+#ifndef STRM_C_FWD_S
+#define STRM_C_FWD_S 4
+#endif
+#ifndef STRM_C_BWD_S
+#define STRM_C_BWD_S 3
+#endif
+#ifndef STRM_C_FWD_MINB
+#define STRM_C_FWD_MINB 1
+#endif
+#ifndef STRM_C_BWD_MINB
+#define STRM_C_BWD_MINB 1
+#endif
+
 template <typename E, int V, bool BWD>
 struct StreamCfg {
-    static constexpr int W = BWD ? STRM_BWD_W : STRM_FWD_W;
-    static constexpr int S = BWD ? STRM_BWD_S : STRM_FWD_S;
-    static constexpr int MINB = BWD ? STRM_BWD_MINB : STRM_FWD_MINB;
-    static constexpr int TSraw = (BWD ? STRM_BWD_BYTES : STRM_FWD_BYTES) / (int)(sizeof(E) * V);
+    static constexpr bool CX = sizeof(E) == 8;
+    static constexpr int W = CX ? (BWD ? STRM_C_BWD_W : STRM_C_FWD_W) : (BWD ? STRM_BWD_W : STRM_FWD_W);
+    static constexpr int S = CX ? (BWD ? STRM_C_BWD_S : STRM_C_FWD_S) : (BWD ? STRM_BWD_S : STRM_FWD_S);
+    static constexpr int MINB = CX ? (BWD ? STRM_C_BWD_MINB : STRM_C_FWD_MINB) : (BWD ? STRM_BWD_MINB : STRM_FWD_MINB);
+    static constexpr int BYTES =
+        CX ? (BWD ? STRM_C_BWD_BYTES : STRM_C_FWD_BYTES) : (BWD ? STRM_BWD_BYTES : STRM_FWD_BYTES);
+    static constexpr int TSraw = BYTES / (int)(sizeof(E) * V);
     static constexpr int TS = TSraw > 16 ? 16 : (TSraw < 1 ? 1 : TSraw);
 };
 
