@@ -68,17 +68,15 @@ __device__ __forceinline__ float ex2_fast(float x) {
 // e < 0.1 (truncation below 2e-7 relative) and log(1 + e) above, where rounding 1 + e costs at
 // most 6e-7 relative: full float32 accuracy for two special-function ops.
 __device__ __forceinline__ float softplus_f(float x) {
-    if (x > 20.f) return x;
-    const float e = __expf(x);
-    if (e < 0.1f) {
-        float p = fmaf(e, -1.f / 6.f, 0.2f);
-        p = fmaf(e, p, -0.25f);
-        p = fmaf(e, p, 1.f / 3.f);
-        p = fmaf(e, p, -0.5f);
-        p = fmaf(e, p, 1.f);
-        return e * p;
-    }
-    return __logf(1.f + e);
+    // both branches are evaluated and selected (a warp nearly always holds inputs of both kinds)
+    const float e = __expf(fminf(x, 20.f));
+    float p = fmaf(e, -1.f / 6.f, 0.2f);
+    p = fmaf(e, p, -0.25f);
+    p = fmaf(e, p, 1.f / 3.f);
+    p = fmaf(e, p, -0.5f);
+    p = fmaf(e, p, 1.f);
+    const float r = e < 0.1f ? e * p : __logf(1.f + e);
+    return (x > 20.f || x != x) ? x : r;  // NaN passes through
 }
 
 // Sum v[0..G) over the TPC lanes of a channel group so that lane `ng` ends with the total of
@@ -140,10 +138,48 @@ __global__ void __launch_bounds__(DB* TPC) mamba_fwd_kernel(const MambaArgs p) {
     for (int e = tid; e < S * STAGE + 2 * kT * DB; e += NTHR) smem[e] = 0.f;  // pads must read as zero
     __syncthreads();
 
+    // Whole tiles of a CTA whose rows are whole 16-byte pieces take a path with no index
+    // arithmetic per tile: every thread copies the same pieces of every tile, so it keeps their
+    // offsets (rows advance by 4 TPC per pass over the threads) and running tile offsets.
+    const bool fastc = VEC == 4 && dcols == DB && N == NPAD;
+    constexpr int PPR4 = DB / 4;                                // 16-byte pieces per [t][d] row
+    constexpr int TD_PIECES = kT * PPR4, N_PIECES = kT * TPC;   // per tensor and tile
+    constexpr int TD_PER = (TD_PIECES + NTHR - 1) / NTHR, N_PER = (N_PIECES + NTHR - 1) / NTHR;
+    const int soff0 = (tid / PPR4) * DB + (tid % PPR4) * 4;
+    const long long goff0 = (long long)(tid / PPR4) * D + (tid % PPR4) * 4;
+    const int soffn0 = (tid / TPC) * NPAD + (tid % TPC) * 4;
+    const long long goffn0 = (long long)(tid / TPC) * N + (tid % TPC) * 4;
+    long long ioff = b * L * D + d0, ioffn = b * L * N;  // next tile to fetch (tiles are fetched in order)
+    long long ooff = b * L * D + d0;                     // next tile to store
+
     auto issue = [&](long long c, int slot) {
         const long long t0 = c * kT;
         const int rows = (int)((L - t0) < kT ? (L - t0) : kT);
         float* st = ring + slot * STAGE;
+        if (fastc && rows == kT) {
+#pragma unroll
+            for (int j = 0; j < TD_PER; ++j) {
+                if (TD_PIECES % NTHR == 0 || tid + j * NTHR < TD_PIECES) {
+                    const long long g = ioff + goff0 + (long long)j * (4 * TPC) * D;
+                    float* sd = st + soff0 + j * (4 * TPC) * DB;
+                    mcp16(sd, p.draw + g);
+                    mcp16(sd + kT * DB, p.u + g);
+                    mcp16(sd + 2 * kT * DB, p.z + g);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < N_PER; ++j) {
+                if (N_PIECES % NTHR == 0 || tid + j * NTHR < N_PIECES) {
+                    const long long g = ioffn + goffn0 + (long long)j * DB * N;
+                    float* sd = st + 3 * kT * DB + soffn0 + j * DB * NPAD;
+                    mcp16(sd, p.Bt + g);
+                    mcp16(sd + kT * NPAD, p.Ct + g);
+                }
+            }
+            ioff += kT * D, ioffn += kT * N;
+            return;
+        }
+        ioff += kT * D, ioffn += kT * N;
         const long long off = (b * L + t0) * D + d0;
         copy_tile<VEC, NTHR>(st, DB, p.draw + off, D, rows, DB, dcols, tid);
         copy_tile<VEC, NTHR>(st + kT * DB, DB, p.u + off, D, rows, DB, dcols, tid);
@@ -156,6 +192,18 @@ __global__ void __launch_bounds__(DB* TPC) mamba_fwd_kernel(const MambaArgs p) {
         const long long t0 = c * kT;
         const int rows = (int)((L - t0) < kT ? (L - t0) : kT);
         const float* ob = outbuf + (c & 1) * kT * DB;
+        if (fastc && rows == kT) {
+#pragma unroll
+            for (int j = 0; j < TD_PER; ++j) {
+                if (TD_PIECES % NTHR == 0 || tid + j * NTHR < TD_PIECES) {
+                    __stcs(reinterpret_cast<float4*>(p.out + ooff + goff0 + (long long)j * (4 * TPC) * D),
+                           *reinterpret_cast<const float4*>(ob + soff0 + j * (4 * TPC) * DB));
+                }
+            }
+            ooff += kT * D;
+            return;
+        }
+        ooff += kT * D;
         float* dst = p.out + (b * L + t0) * D + d0;
         constexpr int PPR = DB / VEC;
         for (int e = tid; e < rows * PPR; e += NTHR) {
@@ -185,21 +233,33 @@ __global__ void __launch_bounds__(DB* TPC) mamba_fwd_kernel(const MambaArgs p) {
     }
     const float Dp = d_ok ? p.Dp[d] : 0.f;
 
-    for (long long c = 0; c < p.NC; ++c) {
-        const int slot = (int)(c % S);
+    int slot = 0, nslot = S - 1;  // stage of tile c and of the tile fetched while it is worked on
+    for (long long c = 0; c < p.NC; ++c, slot = slot + 1 == S ? 0 : slot + 1, nslot = nslot + 1 == S ? 0 : nslot + 1) {
         float* st = ring + slot * STAGE;
         const int tlive = (int)((L - c * kT) < kT ? (L - c * kT) : kT);
         mcp_wait<S - 2>();
         __syncthreads();  // tile c has landed for everyone; tile c-1 is fully consumed and staged
-        if (c + S - 1 < p.NC) issue(c + S - 1, (int)((c + S - 1) % S));
+        if (c + S - 1 < p.NC) issue(c + S - 1, nslot);
         mcp_commit();
         if (c > 0) store_out(c - 1);
 
         // once per (t, d): draw -> delta, z -> z * sigmoid(z)
-        for (int e = tid; e < tlive * DB; e += NTHR) {
-            st[e] = softplus_f(st[e]);
-            const float zz = st[2 * kT * DB + e];
-            st[2 * kT * DB + e] = zz * sigmoid_f(zz);
+        if (tlive == kT) {
+#pragma unroll
+            for (int j = 0; j < (kT * DB + NTHR - 1) / NTHR; ++j) {
+                const int e = tid + j * NTHR;
+                if ((kT * DB) % NTHR == 0 || e < kT * DB) {
+                    st[e] = softplus_f(st[e]);
+                    const float zz = st[2 * kT * DB + e];
+                    st[2 * kT * DB + e] = zz * sigmoid_f(zz);
+                }
+            }
+        } else {
+            for (int e = tid; e < tlive * DB; e += NTHR) {
+                st[e] = softplus_f(st[e]);
+                const float zz = st[2 * kT * DB + e];
+                st[2 * kT * DB + e] = zz * sigmoid_f(zz);
+            }
         }
         __syncthreads();
 
@@ -363,11 +423,57 @@ __global__ void __launch_bounds__(DB* TPC, 4) mamba_bwd_kernel(const MambaArgs p
     for (int e = tid; e < S * STAGE + 4 * TD + NW * kTB * 2 * NPAD; e += NTHR) smem[e] = 0.f;
     __syncthreads();
 
+    // Whole tiles of a CTA whose rows are whole 16-byte pieces take a path with no index
+    // arithmetic per tile (same pieces for every tile, running offsets that step back one tile).
+    const bool fastc = VEC == 4 && dcols == DB && N == NPAD;
+    constexpr int PPR4 = DB / 4;
+    constexpr int TD_PIECES = kTB * PPR4, N_PIECES = kTB * TPC;
+    constexpr int TD_PER = (TD_PIECES + NTHR - 1) / NTHR, N_PER = (N_PIECES + NTHR - 1) / NTHR;
+    const int soff0 = (tid / PPR4) * DB + (tid % PPR4) * 4;
+    const long long goff0 = (long long)(tid / PPR4) * D + (tid % PPR4) * 4;
+    const int soffn0 = (tid / TPC) * NPAD + (tid % TPC) * 4;
+    const long long goffn0 = (long long)(tid / TPC) * N + (tid % TPC) * 4;
+    // offsets of the next tile to fetch / to store (tiles are visited last to first, in order)
+    long long ioff = (b * L + (p.NCB - 1) * kTB) * D + d0, ioffn = (b * L + (p.NCB - 1) * kTB) * N;
+    long long ckoff = ((b * p.NCB + p.NCB - 2) * D + d) * N + n0;
+    long long ooff = ioff, poff = ((dblk * p.B + b) * L + (p.NCB - 1) * kTB) * N;
+
     // tiles are visited from the last to the first: visit index i <-> tile c = NC-1-i
     auto issue = [&](long long c, int slot) {
         const long long t0 = c * kTB;
         const int rows = (int)((L - t0) < kTB ? (L - t0) : kTB);
         float* st = ring + slot * STAGE;
+        if (fastc && rows == kTB) {
+#pragma unroll
+            for (int j = 0; j < TD_PER; ++j) {
+                if (TD_PIECES % NTHR == 0 || tid + j * NTHR < TD_PIECES) {
+                    const long long g = ioff + goff0 + (long long)j * (4 * TPC) * D;
+                    float* sd = st + soff0 + j * (4 * TPC) * DB;
+                    mcp16(sd, p.draw + g);
+                    mcp16(sd + TD, p.u + g);
+                    mcp16(sd + 2 * TD, p.z + g);
+                    mcp16(sd + 3 * TD, p.gout + g);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < N_PER; ++j) {
+                if (N_PIECES % NTHR == 0 || tid + j * NTHR < N_PIECES) {
+                    const long long g = ioffn + goffn0 + (long long)j * DB * N;
+                    float* sd = st + 4 * TD + soffn0 + j * DB * NPAD;
+                    mcp16(sd, p.Bt + g);
+                    mcp16(sd + kTB * NPAD, p.Ct + g);
+                }
+            }
+            float* ck = st + 4 * TD + 2 * kTB * NPAD + 4 * tid;
+            if (c > 0) {
+                mcp16(ck, p.chk + ckoff);
+            } else if (p.h0 != nullptr) {
+                mcp16(ck, p.h0 + (b * D + d) * N + n0);
+            }
+            ioff -= kTB * D, ioffn -= kTB * N, ckoff -= D * N;
+            return;
+        }
+        ioff -= kTB * D, ioffn -= kTB * N, ckoff -= D * N;
         const long long off = (b * L + t0) * D + d0;
         copy_tile<VEC, NTHR>(st, DB, p.draw + off, D, rows, DB, dcols, tid);
         copy_tile<VEC, NTHR>(st + TD, DB, p.u + off, D, rows, DB, dcols, tid);
@@ -430,7 +536,7 @@ __global__ void __launch_bounds__(DB* TPC, 4) mamba_bwd_kernel(const MambaArgs p
         mcp_commit();
 
         // once per (t, d): delta, sigmoid(draw), gy = gout*silu(z), gq = gout*d silu(z)/dz
-        for (int e = tid; e < tlive * DB; e += NTHR) {
+        auto prep = [&](int e) {
             const float x = st[e];
             st[e] = softplus_f(x);
             sigd[e] = sigmoid_f(x);
@@ -438,6 +544,14 @@ __global__ void __launch_bounds__(DB* TPC, 4) mamba_bwd_kernel(const MambaArgs p
             const float sz = sigmoid_f(zz);
             st[2 * TD + e] = go * zz * sz;
             st[3 * TD + e] = go * sz * (1.f + zz * (1.f - sz));
+        };
+        if (tlive == kTB) {
+#pragma unroll
+            for (int j = 0; j < (TD + NTHR - 1) / NTHR; ++j) {
+                if (TD % NTHR == 0 || tid + j * NTHR < TD) prep(tid + j * NTHR);
+            }
+        } else {
+            for (int e = tid; e < tlive * DB; e += NTHR) prep(e);
         }
         __syncthreads();
 
@@ -587,7 +701,31 @@ __global__ void __launch_bounds__(DB* TPC, 4) mamba_bwd_kernel(const MambaArgs p
         __syncthreads();
 
         // staged per-(t,d) gradients -> global; per-warp grad_B/grad_C rows -> this block's partial
-        {
+        if (fastc && tlive == kTB) {
+#pragma unroll
+            for (int j = 0; j < TD_PER; ++j) {
+                if (TD_PIECES % NTHR == 0 || tid + j * NTHR < TD_PIECES) {
+                    const long long g = ooff + goff0 + (long long)j * (4 * TPC) * D;
+                    const float* ob = obuf + soff0 + j * (4 * TPC) * DB;
+                    __stcs(reinterpret_cast<float4*>(p.gdraw + g), *reinterpret_cast<const float4*>(ob));
+                    __stcs(reinterpret_cast<float4*>(p.gu + g), *reinterpret_cast<const float4*>(ob + TD));
+                    __stcs(reinterpret_cast<float4*>(p.gz + g), *reinterpret_cast<const float4*>(ob + 2 * TD));
+                }
+            }
+            // per-warp grad_B / grad_C rows -> this block's partial: element e = (t, which, n)
+#pragma unroll
+            for (int j = 0; j < (kTB * 2 * NPAD + NTHR - 1) / NTHR; ++j) {
+                const int e = tid + j * NTHR;
+                if ((kTB * 2 * NPAD) % NTHR == 0 || e < kTB * 2 * NPAD) {
+                    const int t = e / (2 * NPAD), rem = e % (2 * NPAD);
+                    float sacc = 0.f;
+#pragma unroll
+                    for (int ww = 0; ww < NW; ++ww) sacc += red[(ww * kTB + t) * 2 * NPAD + rem];
+                    float* dst = rem < NPAD ? p.gB_part : p.gC_part;
+                    dst[poff + t * NPAD + (rem % NPAD)] = sacc;
+                }
+            }
+        } else {
             const long long t0 = c * kTB;
             constexpr int PPR = DB / VEC;
             float* dsts[3] = {p.gdraw, p.gu, p.gz};
@@ -619,6 +757,7 @@ __global__ void __launch_bounds__(DB* TPC, 4) mamba_bwd_kernel(const MambaArgs p
                 }
             }
         }
+        ooff -= kTB * D, poff -= kTB * N;
         // the next iteration's first barrier orders these reads before obuf/red are rewritten
     }
     mcp_wait<0>();
