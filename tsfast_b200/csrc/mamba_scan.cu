@@ -233,6 +233,7 @@ __global__ void __launch_bounds__(DB* TPC) mamba_fwd_kernel(const MambaArgs p) {
     }
     const float Dp = d_ok ? p.Dp[d] : 0.f;
 
+    float* ckp = STORE_CHK ? p.chk + (b * p.NCB * D + d) * N + n0 : nullptr;  // next checkpoint slot
     int slot = 0, nslot = S - 1;  // stage of tile c and of the tile fetched while it is worked on
     for (long long c = 0; c < p.NC; ++c, slot = slot + 1 == S ? 0 : slot + 1, nslot = nslot + 1 == S ? 0 : nslot + 1) {
         float* st = ring + slot * STAGE;
@@ -291,8 +292,8 @@ __global__ void __launch_bounds__(DB* TPC) mamba_fwd_kernel(const MambaArgs p) {
         auto store_chk = [&](int t_done) {  // state after step t_done (tile-local) -> its checkpoint slot
             if constexpr (STORE_CHK) {
                 if (d_ok) {
-                    const long long slot_k = (c * kT + t_done + 1) / kTB - 1;
-                    float* ck = p.chk + ((b * p.NCB + slot_k) * D + d) * N + n0;
+                    float* ck = ckp;  // slots are written in order, one every kTB steps
+                    ckp += D * N;
                     if (VEC == 4 && n0 + kNPT <= N) {
                         *reinterpret_cast<float4*>(ck) = make_float4(h[0], h[1], h[2], h[3]);
                     } else {
@@ -525,14 +526,14 @@ __global__ void __launch_bounds__(DB* TPC, 4) mamba_bwd_kernel(const MambaArgs p
     float gDp = 0.f;
     const bool first_has_h0 = p.h0 != nullptr;
 
-    for (long long i = 0; i < p.NCB; ++i) {
+    int slot = 0, nslot = S - 1;  // stage of the tile worked on and of the tile fetched meanwhile
+    for (long long i = 0; i < p.NCB; ++i, slot = slot + 1 == S ? 0 : slot + 1, nslot = nslot + 1 == S ? 0 : nslot + 1) {
         const long long c = p.NCB - 1 - i;
-        const int slot = (int)(i % S);
         float* st = ring + slot * STAGE;
         const int tlive = (int)((L - c * kTB) < kTB ? (L - c * kTB) : kTB);
         mcp_wait<S - 2>();
         __syncthreads();
-        if (i + S - 1 < p.NCB) issue(p.NCB - 1 - (i + S - 1), (int)((i + S - 1) % S));
+        if (i + S - 1 < p.NCB) issue(p.NCB - 1 - (i + S - 1), nslot);
         mcp_commit();
 
         // once per (t, d): delta, sigmoid(draw), gy = gout*silu(z), gq = gout*d silu(z)/dz
