@@ -14,7 +14,8 @@ from pathlib import Path
 import pytest
 import torch
 
-_REF = Path(os.environ.get("TSFAST_CHECKOUT", "/root/reference"))
+# a tsfast checkout: TSFAST_CHECKOUT, else a folder named "reference" beside this repository
+_REF = Path(os.environ.get("TSFAST_CHECKOUT", str(Path(__file__).resolve().parents[2] / "reference")))
 
 
 @pytest.fixture(scope="module")
