@@ -100,6 +100,22 @@ int b200_allpole_fwd(int64_t lanes, int64_t L, int64_t na, const void* a, const 
 int b200_allpole_bwd(int64_t lanes, int64_t L, int64_t na, const void* g, const void* a, const void* y,
                      const void* y0, void* ga, void* gw, void* gy0, void* stream);
 
+/* ---- dynoNet G-block forward: FIR numerator + all-pole denominator + sum over inputs, fused --
+ * For every batch row b and output channel i:  y[b,i,t] = sum_j allpole(a[i,j], w_ij)[t] with
+ * w_ij[t] = sum_{k<nb} taps[i,j,k] * ub[b,j, t + nb-1 - k], where row ub[b,j,:] holds the carried
+ * input tail (nb-1 samples) followed by u[b,:,j] (pitch floats per row, zero filled past
+ * L+nb-1).  Replaces the body of LinearDynamicalOperator.forward for the "scan" backend,
+ * tsfast/models/architectures/dynonet/core.py:199-250 (cat + flipped grouped conv1d :214-220,
+ * the all-pole dispatch :228-231, the new state :240-246 and the pair sum :250), without the
+ * [B, I*O, L] numerator output ever reaching memory.  float32, 1 <= na <= 4, nb in {4, 8, 16}
+ * (pad taps and tail with zeros up to the next size); pairs are indexed j*O + i as in the
+ * reference.  taps [O,I,nb], a [O,I,na], x0 [B,I*O,na] or NULL (newest first), y [B,O,L] (the
+ * reference returns this tensor transposed to [B,L,O] as a view), y_pairs [B,I*O,L] or NULL (the
+ * per-pair outputs the adjoint b200_allpole_bwd needs), x_last [B,I*O,na].  No workspace. */
+int b200_gblock_fwd(int64_t B, int64_t L, int64_t I, int64_t O, int64_t na, int64_t nb, int64_t pitch,
+                    const void* ub, const void* taps, const void* a, const void* x0, void* y, void* y_pairs,
+                    void* x_last, void* stream);
+
 /* ---- S3: fused Mamba selective-scan section ---------------------------------------------
  * delta = softplus(draw) (threshold 20); h_t = exp(delta_t A) h_{t-1} + delta_t u_t B_t;
  * out_t = (h_t . C_t + Dp u_t) * z_t * sigmoid(z_t); hlast = h_L.  All float32.

@@ -158,6 +158,72 @@ def allpole_bwd(g, a, y, y0=None):
     return ga, gw, gy0
 
 
+# ------------------------------------------------------------------ dynoNet G-block (FIR + all-pole + pair sum)
+def gblock_fwd(u, b_coeff, a_coeff, u_tail=None, x0=None):
+    """``LinearDynamicalOperator.forward`` of tsfast/models/architectures/dynonet/core.py:199-250.
+
+    u [B,L,I], b_coeff [O,I,nb], a_coeff [O,I,na], u_tail [B,nb-1,I] or None, x0 [B,I*O,na] or None
+    (pair index j*O + i, newest output first).  Returns ``(y [B,L,O], y_pairs [B,I*O,L],
+    x_last [B,I*O,na], new_tail [B,nb-1,I])``: the numerator is the causal FIR
+    ``w_t = sum_k b_k u_{t-k}`` on ``cat(u_tail, u)`` (:214-220), the denominator the all-pole
+    recurrence (:228-231), ``x_last`` the last ``na`` outputs reversed, padded from ``x0`` when the
+    chunk is shorter than ``na`` (:240-246), and the output the sum over inputs (:250).
+    """
+    u, b_coeff, a_coeff = _c(u), _c(b_coeff), _c(a_coeff)
+    B, L, I = u.shape
+    O, _, nb = b_coeff.shape
+    na = a_coeff.shape[-1]
+    P = I * O
+    dt = u.dtype
+    tail = np.zeros((B, nb - 1, I), dt) if u_tail is None else np.asarray(u_tail, dt)
+    ubuf = np.concatenate((tail, u), axis=1)  # [B, L+nb-1, I]
+    w = np.zeros((B, P, L), dt)
+    for j in range(I):
+        for i in range(O):
+            acc = np.zeros((B, L), dt)
+            for k in range(nb):
+                acc += b_coeff[i, j, k] * ubuf[:, nb - 1 - k : nb - 1 - k + L, j]
+            w[:, j * O + i] = acc
+    a_pairs = np.ascontiguousarray(np.broadcast_to(a_coeff.transpose(1, 0, 2).reshape(1, P, na), (B, P, na))).reshape(B * P, na)
+    y0 = None if x0 is None else np.ascontiguousarray(np.asarray(x0, dt)).reshape(B * P, na)
+    yp = allpole_fwd(a_pairs, w.reshape(B * P, L), y0).reshape(B, P, L)
+    y = yp.reshape(B, I, O, L).sum(1).transpose(0, 2, 1)
+    x0z = np.zeros((B, P, na), dt) if x0 is None else np.asarray(x0, dt)
+    hist = np.concatenate((x0z[..., ::-1], yp), axis=-1)  # oldest .. newest
+    x_last = np.ascontiguousarray(hist[..., ::-1][..., :na])
+    new_tail = ubuf[:, ubuf.shape[1] - (nb - 1) :]
+    return np.ascontiguousarray(y), yp, x_last, np.ascontiguousarray(new_tail)
+
+
+def gblock_bwd(gy, u, b_coeff, a_coeff, y_pairs, u_tail=None, x0=None):
+    """Adjoint of ``gblock_fwd`` for an upstream gradient on ``y`` only: returns
+    ``(gu [B,L,I], gb [O,I,nb], ga [O,I,na], gu_tail [B,nb-1,I], gx0 [B,I*O,na] | None)``."""
+    gy, u, b_coeff, a_coeff, y_pairs = _c(gy), _c(u), _c(b_coeff), _c(a_coeff), _c(y_pairs)
+    B, L, I = u.shape
+    O, _, nb = b_coeff.shape
+    na = a_coeff.shape[-1]
+    P = I * O
+    dt = u.dtype
+    g_pairs = np.ascontiguousarray(np.broadcast_to(gy.transpose(0, 2, 1)[:, None], (B, I, O, L))).reshape(B * P, L)
+    a_pairs = np.ascontiguousarray(np.broadcast_to(a_coeff.transpose(1, 0, 2).reshape(1, P, na), (B, P, na))).reshape(B * P, na)
+    y0 = None if x0 is None else np.ascontiguousarray(np.asarray(x0, dt)).reshape(B * P, na)
+    ga_l, gw, gy0 = allpole_bwd(g_pairs, a_pairs, y_pairs.reshape(B * P, L), y0)
+    gw = gw.reshape(B, I, O, L)
+    tail = np.zeros((B, nb - 1, I), dt) if u_tail is None else np.asarray(u_tail, dt)
+    ubuf = np.concatenate((tail, u), axis=1)
+    gubuf = np.zeros_like(ubuf)
+    gb = np.zeros_like(b_coeff)
+    for j in range(I):
+        for i in range(O):
+            for k in range(nb):
+                seg = slice(nb - 1 - k, nb - 1 - k + L)
+                gb[i, j, k] = np.sum(gw[:, j, i] * ubuf[:, seg, j])
+                gubuf[:, seg, j] += b_coeff[i, j, k] * gw[:, j, i]
+    ga = ga_l.reshape(B, I, O, na).sum(0).transpose(1, 0, 2)
+    gx0 = None if gy0 is None else gy0.reshape(B, P, na)
+    return np.ascontiguousarray(gubuf[:, nb - 1 :]), gb, np.ascontiguousarray(ga), np.ascontiguousarray(gubuf[:, : nb - 1]), gx0
+
+
 # ------------------------------------------------------------------ Mamba causal conv + SiLU
 def conv_fwd(x, tail, w, bias=None):
     """``silu(conv1d(cat(tail, x)))`` depthwise and causal: x [B,L,D], tail [B,D,K-1], w [D,K], bias [D]."""

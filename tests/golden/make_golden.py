@@ -309,9 +309,50 @@ def make_conv():
     print("conv", len(names), "cases")
 
 
+# ------------------------------------------------------------------ dynoNet G-block
+def make_gblock():
+    """The reference's ``LinearDynamicalOperator`` (tsfast/models/architectures/dynonet/core.py:
+    144-254) in float64 on its CPU path: output, new state, and the gradient of ``sum(y * g)``
+    w.r.t. the input, both coefficient tensors and the carried state."""
+    from tsfast.models.architectures.dynonet.core import LinearDynamicalOperator
+
+    # (B, L, I, O, nb, na, with_state)
+    cases = [(2, 50, 1, 3, 8, 2, False), (2, 130, 3, 2, 8, 2, True), (1, 1100, 2, 2, 4, 4, True),
+             (2, 33, 2, 1, 5, 3, True), (1, 3, 1, 1, 8, 4, True), (2, 64, 4, 4, 16, 1, False),
+             (3, 257, 2, 3, 8, 4, True)]
+    store, names = {}, []
+    for idx, (Bsz, L, I, O, nb, na, with_state) in enumerate(cases):
+        gen = torch.Generator().manual_seed(5000 + idx)
+        op = LinearDynamicalOperator(I, O, nb=nb, na=na, backend="scan").double()
+        with torch.no_grad():
+            op.b_coeff.copy_((torch.randn(O, I, nb, generator=gen) * 0.3).double())  # float32 values
+            op.a_coeff.copy_((torch.randn(O, I, na, generator=gen) * 0.2).double())
+        u = torch.randn(Bsz, L, I, generator=gen)
+        g = torch.randn(Bsz, L, O, generator=gen)
+        tail = torch.randn(Bsz, nb - 1, I, generator=gen) if with_state else None
+        x0 = torch.randn(Bsz, I * O, na, generator=gen) if with_state else None
+        u_, tail_, x0_ = _leaf(_to64(u)), _leaf(_to64(tail)), _leaf(_to64(x0))
+        state = {"u": tail_, "x": x0_} if with_state else None
+        y, new_state = op(u_, state=state, return_state=True)
+        (y * _to64(g)).sum().backward()
+        name = f"case{idx}"
+        names.append(name)
+        store.update({f"{name}_u": _np(u), f"{name}_g": _np(g), f"{name}_b": _np(op.b_coeff.float()),
+                      f"{name}_a": _np(op.a_coeff.float()), f"{name}_ref64_y": _np(y),
+                      f"{name}_ref64_tail": _np(new_state["u"]), f"{name}_ref64_xlast": _np(new_state["x"]),
+                      f"{name}_ref64_gu": _np(u_.grad), f"{name}_ref64_gb": _np(op.b_coeff.grad),
+                      f"{name}_ref64_ga": _np(op.a_coeff.grad)})
+        if with_state:
+            store.update({f"{name}_tail": _np(tail), f"{name}_x0": _np(x0),
+                          f"{name}_ref64_gtail": _np(tail_.grad), f"{name}_ref64_gx0": _np(x0_.grad)})
+    store["names"] = np.array(names)
+    np.savez_compressed(HERE / "gblock.npz", **store)
+    print("gblock", len(names), "cases")
+
+
 if __name__ == "__main__":
     torch.set_num_threads(4)
-    which = sys.argv[1:] or ["diag", "sel", "mamba", "allpole", "lru", "conv"]
+    which = sys.argv[1:] or ["diag", "sel", "mamba", "allpole", "lru", "conv", "gblock"]
     if "diag" in which:
         make_diag("diag")
     if "sel" in which:
@@ -324,3 +365,5 @@ if __name__ == "__main__":
         make_lru()
     if "conv" in which:
         make_conv()
+    if "gblock" in which:
+        make_gblock()

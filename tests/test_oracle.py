@@ -94,6 +94,24 @@ def test_conv(oracle, f64):
             assert rel_err(gb, c.ref64_gb) < tol, (c.name, "gb")
 
 
+@pytest.mark.parametrize("f64", [True, False])
+def test_gblock(oracle, f64):
+    """FIR numerator + all-pole denominator + pair sum against the reference's LinearDynamicalOperator."""
+    tol = TOL64 if f64 else TOL32
+    for c in load_golden("gblock"):
+        u, b, a, tail, x0, g = (_cast(t, f64) for t in (c.u, c.b, c.a, c.tail, c.x0, c.g))
+        y, yp, xl, nt = oracle.gblock_fwd(u, b, a, tail, x0)
+        assert rel_err(y, c.ref64_y) < tol, (c.name, "y")
+        assert rel_err(xl, c.ref64_xlast) < tol, (c.name, "xlast")
+        assert rel_err(nt, c.ref64_tail) < tol, (c.name, "tail")
+        gu, gb, ga, gt, gx0 = oracle.gblock_bwd(g, u, b, a, yp, tail, x0)
+        for k, v in (("gu", gu), ("gb", gb), ("ga", ga)):
+            assert rel_err(v, getattr(c, "ref64_" + k)) < tol, (c.name, k)
+        if tail is not None:
+            assert rel_err(gt, c.ref64_gtail) < tol, (c.name, "gtail")
+            assert rel_err(gx0, c.ref64_gx0) < tol, (c.name, "gx0")
+
+
 def test_allpole_unstable_pole_overflows_without_crash(oracle):
     """An unstable filter must run to non-finite values, not fault (reference tests/test_dynonet.py:165-174)."""
     a = np.array([[-3.0]], dtype=np.float32)

@@ -441,9 +441,385 @@ static int run_allpole(bool bwd, long long lanes, long long L, long long na, con
     return vec ? dispatch_na<false, 4>((int)na, p, st) : dispatch_na<false, 1>((int)na, p, st);
 }
 
+
+// =============================================================================== fused G-block
+// dynoNet's linear block for one (batch row, output channel): for every input channel j the FIR
+// numerator w = b_ij * u_j (causal, NB taps, the carried input tail in front of the row), the
+// all-pole denominator 1/A_ij on w, and the sum of the filtered signals over j.  Neither w nor
+// (unless asked for) the per-pair outputs touch HBM: one warp owns (b, i), walks time in tiles of
+// 1024 steps and, inside a tile, the input channels one after the other, adding each pair's
+// output into 32 registers per thread.  The all-pole part is the scheme of allpole_kernel above
+// (segment maps composed by a warp-shuffle Kogge-Stone scan in float64) with the matrix powers
+// and the carried state of every pair kept in shared memory.
+struct GBlockArgs {
+    const float* ub;   // [B*I, pitch]: row (b, j) = carried tail (NB-1 samples) followed by u[b, :, j]
+    const float* taps; // [O, I, NB] numerator taps b_0 .. b_{NB-1} (zero padded)
+    const float* a;    // [O, I, na]
+    const float* x0;   // [B, I*O, na] or null; pair index j*O + i
+    float* y;          // [B, O, L]
+    float* yp;         // [B, I*O, L] or null: the per-pair outputs (what the adjoint needs)
+    float* xlast;      // [B, I*O, na]: last na outputs of every pair, newest first
+    long long B, I, O, L, pitch;
+};
+
+template <int NA, int NB, int VEC, int W, int S>
+__global__ void __launch_bounds__(32 * W, 4) gblock_fwd_kernel(const GBlockArgs p) {
+    constexpr int kSeg = 32, kTile = 32 * kSeg, kChunk = kSeg + 4;
+    constexpr int kStageF = 33 * kChunk;  // 32 thread chunks + one for the NB-1 samples past the tile
+    constexpr int PIECES = kTile / VEC, PPC = kSeg / VEC;
+    constexpr int HALO = (NB - 1 + VEC - 1) / VEC;  // copy pieces past the tile
+    constexpr int NU = kSeg + NB - 1;               // samples a thread's segment reads
+    static_assert(NB >= 1 && NB - 1 <= kSeg, "the halo must fit one chunk");
+
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int w = threadIdx.x >> 5, lid = threadIdx.x & 31;
+    const long long widx = (long long)blockIdx.x * W + w;
+    if (widx >= p.B * p.O) return;  // warps never synchronise with each other
+    const long long b = widx / p.O, i = widx - b * p.O;
+    const int I = (int)p.I;
+    const long long L = p.L, P = p.I * p.O;
+
+    // per warp: doubles [2 NA^2 scratch | I x 5 NA^2 powers | I x NA carried states], then floats
+    // [S ring stages | one stage for the summed output | I x NA previous-tile tails]
+    const int dper = ((2 * NA * NA + I * (5 * NA * NA + NA)) + 1) & ~1;
+    const int fper = S * kStageF + 32 * kChunk + ((I * NA + 3) & ~3);
+    double* Md = reinterpret_cast<double*>(smem_raw) + (size_t)w * dper;
+    double* Mp = Md + 2 * NA * NA;          // [I][5][NA*NA]
+    double* cins = Mp + I * 5 * NA * NA;    // [I][NA]
+    float* fbase = reinterpret_cast<float*>(reinterpret_cast<double*>(smem_raw) + (size_t)W * dper) + (size_t)w * fper;
+    float* ring = fbase;                    // [S][33][kChunk]
+    float* ysum = ring + S * kStageF;       // [32][kChunk]
+    float* ptail = ysum + 32 * kChunk;      // [I][NA]
+
+    const long long C = (L + kTile - 1) / kTile;
+    const long long items = C * I;  // item q = (tile q / I, input channel q % I)
+
+    auto issue = [&](long long q, int slot) {
+        const long long c = q / I, j = q - c * I;
+        const float* src = p.ub + (b * I + j) * p.pitch + c * kTile;
+        const long long room = p.pitch - c * kTile;  // samples of the row from the tile start on
+        float* dst = ring + slot * kStageF;
+#pragma unroll
+        for (int r = 0; r < PIECES / 32; ++r) {
+            const int gidx = r * 32 + lid;
+            if ((long long)gidx * VEC < room) {
+                float* d = dst + (gidx / PPC) * kChunk + (gidx % PPC) * VEC;
+                if constexpr (VEC == 4) cp_async16(d, src + gidx * VEC);
+                else cp_async4(d, src + gidx * VEC);
+            }
+        }
+        if (lid < HALO && (long long)(kTile + lid * VEC) < room) {
+            float* d = dst + 32 * kChunk + lid * VEC;
+            if constexpr (VEC == 4) cp_async16(d, src + kTile + lid * VEC);
+            else cp_async4(d, src + kTile + lid * VEC);
+        }
+    };
+#pragma unroll
+    for (int q = 0; q < S - 1; ++q) {
+        if (q < items) issue(q, q);
+        cp_commit();
+    }
+
+    // ---------------------------------------------------------------- per pair: M^(2^d), start state
+    for (int j = 0; j < I; ++j) {
+        float aj[NA];
+#pragma unroll
+        for (int k = 0; k < NA; ++k) aj[k] = p.a[(i * p.I + j) * NA + k];
+        if (lid < NA) {
+            double s[NA];
+#pragma unroll
+            for (int k = 0; k < NA; ++k) s[k] = (k == lid) ? 1.0 : 0.0;
+            for (int t = 0; t < kSeg; ++t) {
+                double acc = 0.0;
+#pragma unroll
+                for (int k = 0; k < NA; ++k) acc += (double)aj[k] * s[k];
+#pragma unroll
+                for (int k = NA - 1; k >= 1; --k) s[k] = s[k - 1];
+                s[0] = -acc;
+            }
+#pragma unroll
+            for (int r = 0; r < NA; ++r) Md[r * NA + lid] = s[r];
+            const long long pr = b * P + j * p.O + i;
+            cins[j * NA + lid] = p.x0 != nullptr ? (double)p.x0[pr * NA + lid] : 0.0;
+            ptail[j * NA + lid] = 0.f;
+        }
+        __syncwarp();
+        int cur = 0;
+        for (int d = 0; d < 5; ++d) {
+            const double* src = Md + cur * NA * NA;
+            double* dst = Md + (cur ^ 1) * NA * NA;
+            for (int e = lid; e < NA * NA; e += 32) {
+                Mp[(j * 5 + d) * NA * NA + e] = clamp_finite(src[e]);
+                if (d < 4) {
+                    const int r = e / NA, cc = e % NA;
+                    double acc = 0.0;
+                    for (int k = 0; k < NA; ++k) acc += src[r * NA + k] * src[k * NA + cc];
+                    dst[e] = acc;
+                }
+            }
+            __syncwarp();
+            cur ^= 1;
+        }
+    }
+
+    float yacc[kSeg];
+    long long q = 0;
+    for (long long c = 0; c < C; ++c) {
+        const long long t0 = c * kTile;
+        const long long tbase = t0 + lid * kSeg;
+        const bool edge = t0 + kTile > L;
+#pragma unroll
+        for (int r = 0; r < kSeg; ++r) yacc[r] = 0.f;
+        for (int j = 0; j < I; ++j, ++q) {
+            const int slot = (int)(q % S);
+            float* stage = ring + slot * kStageF;
+            cp_wait<S - 2>();
+            __syncwarp();
+
+            // this thread's samples: its own chunk and the first NB-1 of the next one
+            float uc[NU];
+#pragma unroll
+            for (int r = 0; r < kSeg / 4; ++r) {
+                const float4 t4 = *reinterpret_cast<const float4*>(stage + lid * kChunk + 4 * r);
+                uc[4 * r] = t4.x, uc[4 * r + 1] = t4.y, uc[4 * r + 2] = t4.z, uc[4 * r + 3] = t4.w;
+            }
+#pragma unroll
+            for (int r = 0; r < (NB - 1 + 3) / 4; ++r) {
+                const float4 t4 = *reinterpret_cast<const float4*>(stage + (lid + 1) * kChunk + 4 * r);
+                const float t[4] = {t4.x, t4.y, t4.z, t4.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    if (4 * r + e < NB - 1) uc[kSeg + 4 * r + e] = t[e];
+            }
+            __syncwarp();  // everyone has read this stage before the next item's copies may land
+            if (q + S - 1 < items) issue(q + S - 1, (int)((q + S - 1) % S));
+            cp_commit();
+
+            float a[NA], bt[NB];
+#pragma unroll
+            for (int k = 0; k < NA; ++k) a[k] = p.a[(i * p.I + j) * NA + k];
+#pragma unroll
+            for (int k = 0; k < NB; ++k) bt[k] = p.taps[(i * p.I + j) * NB + k];
+
+            // numerator: w_t = sum_k b_k u_buf[t + NB-1 - k]; steps past the sequence get zero
+            float v[kSeg];
+#pragma unroll
+            for (int r = 0; r < kSeg; ++r) {
+                float acc = 0.f;
+#pragma unroll
+                for (int k = NB - 1; k >= 0; --k) acc = fmaf(bt[k], uc[r + NB - 1 - k], acc);
+                v[r] = (!edge || tbase + r < L) ? acc : 0.f;
+            }
+
+            // 1. zero-state response of this thread's segment
+            float s[NA];
+#pragma unroll
+            for (int k = 0; k < NA; ++k) s[k] = 0.f;
+#pragma unroll
+            for (int k = 0; k < kSeg; ++k) iir_step<NA>(a, s, v[k]);
+
+            // 2. carry of the previous tile enters at thread 0; Kogge-Stone over the 32 segments
+            const double* Mj = Mp + j * 5 * NA * NA;
+            double cin[NA], sd[NA];
+#pragma unroll
+            for (int k = 0; k < NA; ++k) {
+                cin[k] = cins[j * NA + k];
+                sd[k] = (double)s[k];
+            }
+            if (lid == 0) {
+#pragma unroll
+                for (int r = 0; r < NA; ++r) {
+                    double t = sd[r];
+#pragma unroll
+                    for (int k = 0; k < NA; ++k) t = fma(Mj[r * NA + k], cin[k], t);
+                    sd[r] = t;
+                }
+            }
+#pragma unroll
+            for (int d = 0; d < 5; ++d) {
+                double sp[NA];
+#pragma unroll
+                for (int k = 0; k < NA; ++k) sp[k] = __shfl_up_sync(0xffffffffu, sd[k], 1 << d);
+                if (lid >= (1 << d)) {
+                    const double* M = Mj + d * NA * NA;
+#pragma unroll
+                    for (int r = 0; r < NA; ++r) {
+                        double t = sd[r];
+#pragma unroll
+                        for (int k = 0; k < NA; ++k) t = fma(M[r * NA + k], sp[k], t);
+                        sd[r] = t;
+                    }
+                }
+            }
+            float st[NA];
+#pragma unroll
+            for (int k = 0; k < NA; ++k) {
+                const double up = __shfl_up_sync(0xffffffffu, sd[k], 1);
+                st[k] = (float)(lid == 0 ? cin[k] : up);
+            }
+#pragma unroll
+            for (int k = 0; k < NA; ++k) {
+                const double e = __shfl_sync(0xffffffffu, sd[k], 31);
+                if (lid == 0) cins[j * NA + k] = e;
+            }
+
+            // 3. the true run of the segment; add the pair's output to the channel sum
+#pragma unroll
+            for (int k = 0; k < kSeg; ++k) {
+                v[k] = iir_step<NA>(a, st, v[k]);
+                yacc[k] += v[k];
+            }
+
+            // stage the pair's tile: per-pair store (if asked for) and the block's new state
+#pragma unroll
+            for (int r = 0; r < kSeg / 4; ++r)
+                *reinterpret_cast<float4*>(stage + lid * kChunk + 4 * r) =
+                    make_float4(v[4 * r], v[4 * r + 1], v[4 * r + 2], v[4 * r + 3]);
+            __syncwarp();
+            const long long pr = b * P + j * p.O + i;
+            if (p.yp != nullptr) {
+                float* out = p.yp + pr * L;
+#pragma unroll
+                for (int r = 0; r < PIECES / 32; ++r) {
+                    const int gidx = r * 32 + lid;
+                    const long long t = t0 + (long long)gidx * VEC;
+                    if (t < L) {
+                        const float* sp = stage + (gidx / PPC) * kChunk + (gidx % PPC) * VEC;
+                        if constexpr (VEC == 4) __stcs(reinterpret_cast<float4*>(out + t), *reinterpret_cast<const float4*>(sp));
+                        else __stcs(out + t, *sp);
+                    }
+                }
+            }
+            if (lid < NA) {  // x_last[k] = y_{L-1-k}; older ones come from the previous tile or x0
+                if (c == C - 1) {
+                    const long long t = L - 1 - lid;
+                    float val;
+                    if (t >= t0) {
+                        const int x = (int)(t - t0);
+                        val = stage[(x / kSeg) * kChunk + (x % kSeg)];
+                    } else if (t >= 0) {
+                        val = ptail[j * NA + (int)(t0 - 1 - t)];
+                    } else {
+                        val = p.x0 != nullptr ? p.x0[pr * NA + (int)(-t - 1)] : 0.f;
+                    }
+                    p.xlast[pr * NA + lid] = val;
+                }
+            }
+            __syncwarp();
+            if (lid < NA && c < C - 1) {  // tail of a whole tile: y_{t0+1023-k}
+                const int x = kTile - 1 - lid;
+                ptail[j * NA + lid] = stage[(x / kSeg) * kChunk + (x % kSeg)];
+            }
+            __syncwarp();
+        }
+        // the channel's tile: stage and store coalesced
+#pragma unroll
+        for (int r = 0; r < kSeg / 4; ++r)
+            *reinterpret_cast<float4*>(ysum + lid * kChunk + 4 * r) =
+                make_float4(yacc[4 * r], yacc[4 * r + 1], yacc[4 * r + 2], yacc[4 * r + 3]);
+        __syncwarp();
+        float* out = p.y + (b * p.O + i) * L;
+#pragma unroll
+        for (int r = 0; r < PIECES / 32; ++r) {
+            const int gidx = r * 32 + lid;
+            const long long t = t0 + (long long)gidx * VEC;
+            if (t < L) {
+                const float* sp = ysum + (gidx / PPC) * kChunk + (gidx % PPC) * VEC;
+                if constexpr (VEC == 4) __stcs(reinterpret_cast<float4*>(out + t), *reinterpret_cast<const float4*>(sp));
+                else __stcs(out + t, *sp);
+            }
+        }
+        __syncwarp();
+    }
+    cp_wait<0>();
+}
+
+#ifndef GBLOCK_W
+#define GBLOCK_W 2  // (batch row, output channel) warps per CTA
+#endif
+#ifndef GBLOCK_S
+#define GBLOCK_S 3  // ring stages per warp
+#endif
+
+template <int NA, int NB, int VEC>
+static int launch_gblock(const GBlockArgs& a, cudaStream_t st) {
+    constexpr int W = GBLOCK_W, S = GBLOCK_S;
+    const int I = (int)a.I;
+    const size_t dper = (size_t)(((2 * NA * NA + I * (5 * NA * NA + NA)) + 1) & ~1);
+    const size_t fper = (size_t)S * 33 * 36 + 32 * 36 + (size_t)((I * NA + 3) & ~3);
+    const size_t smem = W * (dper * sizeof(double) + fper * sizeof(float));
+    if (smem > 200 * 1024) return B200_ERR_UNSUPPORTED;
+    auto kern = gblock_fwd_kernel<NA, NB, VEC, W, S>;
+    static size_t configured[64] = {0};  // largest size asked for so far, per device
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && configured[dev] < smem) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return B200_ERR_LAUNCH;
+        configured[dev] = smem;
+    }
+    const long long grid = (a.B * a.O + W - 1) / W;
+    if (grid > 0x7fffffffLL) return B200_ERR_UNSUPPORTED;
+    kern<<<(unsigned int)grid, 32 * W, smem, st>>>(a);
+    return cudaGetLastError() == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
+}
+
+template <int NA, int VEC>
+static int dispatch_gblock_nb(int nb, const GBlockArgs& a, cudaStream_t st) {
+    switch (nb) {
+        case 4: return launch_gblock<NA, 4, VEC>(a, st);
+        case 8: return launch_gblock<NA, 8, VEC>(a, st);
+        case 16: return launch_gblock<NA, 16, VEC>(a, st);
+        default: return B200_ERR_UNSUPPORTED;
+    }
+}
+
+template <int VEC>
+static int dispatch_gblock(int na, int nb, const GBlockArgs& a, cudaStream_t st) {
+    switch (na) {
+        case 1: return dispatch_gblock_nb<1, VEC>(nb, a, st);
+        case 2: return dispatch_gblock_nb<2, VEC>(nb, a, st);
+        case 3: return dispatch_gblock_nb<3, VEC>(nb, a, st);
+        case 4: return dispatch_gblock_nb<4, VEC>(nb, a, st);
+        default: return B200_ERR_UNSUPPORTED;
+    }
+}
+
 }  // namespace b200
 
 extern "C" {
+int b200_gblock_fwd(int64_t B, int64_t L, int64_t I, int64_t O, int64_t na, int64_t nb, int64_t pitch,
+                    const void* ub, const void* taps, const void* a, const void* x0, void* y, void* y_pairs,
+                    void* x_last, void* stream) {
+    using namespace b200;
+    if (B < 0 || L < 0 || I < 1 || O < 1 || na < 1 || nb < 1 || pitch < L + nb - 1) return B200_ERR_ARG;
+    if (na > 4 || (nb != 4 && nb != 8 && nb != 16)) return B200_ERR_UNSUPPORTED;
+    if (B == 0) return B200_OK;
+    if (!ub || !taps || !a || !x_last || (L > 0 && !y)) return B200_ERR_ARG;
+    const uintptr_t por = (uintptr_t)ub | (uintptr_t)taps | (uintptr_t)a | (uintptr_t)x0 | (uintptr_t)y |
+                          (uintptr_t)y_pairs | (uintptr_t)x_last;
+    if (por % 4 != 0) return B200_ERR_ARG;
+    GBlockArgs p;
+    p.ub = static_cast<const float*>(ub);
+    p.taps = static_cast<const float*>(taps);
+    p.a = static_cast<const float*>(a);
+    p.x0 = static_cast<const float*>(x0);
+    p.y = static_cast<float*>(y);
+    p.yp = static_cast<float*>(y_pairs);
+    p.xlast = static_cast<float*>(x_last);
+    p.B = B, p.I = I, p.O = O, p.L = L, p.pitch = pitch;
+    const uintptr_t seq_or = (uintptr_t)ub | (uintptr_t)y | (uintptr_t)y_pairs;
+    const bool vec = (L % 4 == 0) && (pitch % 4 == 0) && (seq_or % 16 == 0);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (L == 0) {  // an empty chunk leaves the state as it was
+        const size_t bytes = (size_t)B * I * O * na * sizeof(float);
+        const cudaError_t e = x0 ? cudaMemcpyAsync(x_last, x0, bytes, cudaMemcpyDeviceToDevice, st)
+                                 : cudaMemsetAsync(x_last, 0, bytes, st);
+        return e == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
+    }
+    return vec ? dispatch_gblock<4>((int)na, (int)nb, p, st) : dispatch_gblock<1>((int)na, (int)nb, p, st);
+}
+
 
 int b200_allpole_fwd(int64_t lanes, int64_t L, int64_t na, const void* a, const void* w, const void* y0,
                      void* y, void* stream) {
