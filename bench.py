@@ -13,7 +13,7 @@ same metric through the public API from pinned HOST buffers with the host<->devi
 the timed region, `roofline` the dominant kernel (the adjoint) against the measured HBM peak, and
 `cpu_baseline` the CPU oracle (a C port of the reference's CPU kernels) on the host cores.
 `--impl reference` times that CPU port alone and prints the same line shape.
-`--workload C1|C3|C4|C5` measures the other configurations the same way (complex LRU scan, Mamba
+`--workload C1|C3|C4|C5|G` measures the other configurations the same way (complex LRU scan, Mamba
 section, all-pole filter, DeepLRU data-parallel training step); C2 is the headline.
 """
 
@@ -458,6 +458,74 @@ def _workload(name, torch, dev, rank):
                     h2d=2 * E, d2h=2 * E, dtype="f32", launches=2, kernel="allpole_kernel<NA=4, adjoint> (b200_allpole_bwd)",
                     fwd=lambda: allpole_b200._allpole_op(a, w, None), bwd=lambda o: allpole_b200._allpole_bwd_op(g, a, o, None),
                     e2e=e2e, cpu=cpu)
+    if name == "G":
+        from tsfast_b200 import dynonet_b200
+
+        Bn, L, I, O, nb, na = 128, 8192, 8, 16, 8, 4
+        P = I * O
+        rng = np.random.default_rng(4321 + rank)
+        a0 = np.zeros((O, I, na))
+        for i in range(O):
+            for j in range(I):
+                poles = []
+                for _ in range(2):
+                    rr, th = rng.uniform(0.5, 0.95), rng.uniform(0, np.pi)
+                    poles += [rr * np.exp(1j * th), rr * np.exp(-1j * th)]
+                a0[i, j] = np.real(np.poly(poles))[1:]
+        a_c = torch.from_numpy(a0.astype(np.float32)).to(dev).requires_grad_()
+        b_c = (rn(O, I, nb) * 0.3).requires_grad_()
+        u = rn(Bn, L, I).requires_grad_()
+        gy = rn(Bn, L, O)
+        hu, hgy, hy, hgu = pin(u.detach()), pin(gy), pin(gy), pin(u.detach())
+
+        def fwd():
+            return dynonet_b200.linear_block(u, b_c, a_c, None)[0]
+
+        def bwd(y):
+            return torch.autograd.grad(y, (u, b_c, a_c), gy, retain_graph=True)  # timed repeatedly on one graph
+
+        def unfused():  # the reference's formulation with this package's all-pole op in the middle
+            import torch.nn.functional as F
+            with torch.no_grad():
+                u_buf = torch.cat((u.new_zeros(Bn, nb - 1, I), u), 1)
+                weight = b_c.permute(1, 0, 2).reshape(P, 1, nb).flip(-1)
+                w_ = F.conv1d(u_buf.transpose(1, 2), weight, groups=I)
+                yp = allpole_b200.run(a_c.permute(1, 0, 2).reshape(P, na), w_, None)
+                return yp.view(Bn, I, O, L).sum(1).transpose(1, 2)
+
+        def extra(timed):
+            unfused()  # the first grouped conv1d call picks its algorithm
+            with torch.no_grad():
+                fused_ms = timed(lambda: dynonet_b200.linear_block(u, b_c, a_c, None), 5)
+            return {"forward_no_grad_ms": round(fused_ms, 4), "forward_unfused_ms": round(timed(unfused, 5), 4),
+                    "unfused": "grouped conv1d + b200 all-pole op + sum over inputs, as dynonet/core.py:214-250"}
+
+        def e2e():
+            du = hu.to(dev, non_blocking=True).requires_grad_()
+            bb, aa = b_c.detach().clone().requires_grad_(), a_c.detach().clone().requires_grad_()
+            y = dynonet_b200.linear_block(du, bb, aa, None)[0]
+            y.backward(hgy.to(dev, non_blocking=True))
+            hy.copy_(y.detach(), non_blocking=True)
+            hgu.copy_(du.grad, non_blocking=True)
+            return bb.grad.cpu()
+
+        def cpu(rows):
+            from oracle import oracle as O_
+            u_, g_ = u.detach()[:rows].cpu().numpy(), gy[:rows].cpu().numpy()
+            b_, a_ = b_c.detach().cpu().numpy(), a_c.detach().cpu().numpy()
+
+            def run():
+                y, yp, _, _ = O_.gblock_fwd(u_, b_, a_)
+                return O_.gblock_bwd(g_, u_, b_, a_, yp)
+            return run
+
+        E = Bn * L * 4
+        return dict(desc="G: dynoNet G-block (FIR nb=8 + all-pole na=4 + sum over inputs) training step, B=128 T=8192, "
+                         "8 inputs x 16 outputs = 128 filters, fp32",
+                    fwd_bytes=E * (I + O + P), bwd_bytes=E * (O + P + 2 * I), elems=2 * Bn * P * L, rows=Bn, sample_rows=2,
+                    flush=False, h2d=E * (I + O), d2h=E * (I + O), dtype="f32", launches=3,
+                    kernel="allpole_kernel<NA=4, adjoint, row map> + gblock_num_bwd_kernel (b200_gblock_bwd)",
+                    fwd=fwd, bwd=bwd, e2e=e2e, cpu=cpu, extra=extra)
     raise SystemExit(f"unknown workload {name}")
 
 
@@ -539,6 +607,7 @@ def run_workload(args):
                     "kind": "port", "sample": f"{rows} of {wl['rows']} batch rows, fwd+bwd, median of {cnt} passes of "
                     f"{sec * 1e3:.1f} ms; float32 C port of the reference's CPU algorithm, OpenMP"}
         bwd_gbs, fwd_gbs = wl["bwd_bytes"] / bwd_ms / 1e6, wl["fwd_bytes"] / fwd_ms / 1e6
+        extra = wl["extra"](timed) if "extra" in wl else {}
         _emit({
             "metric": METRIC, "value": round(step_bytes * world / ms / 1e6, 1), "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True,
@@ -547,7 +616,8 @@ def run_workload(args):
                        "state_elements_per_s": round(wl["elems"] * world / (ms * 1e-3)),
                        "l2": ("working set fits in L2: a 256 MB buffer is rewritten before every timed call"
                               if wl["flush"] else "streamed tensors are larger than the 126 MB L2; no flush needed"),
-                       "timing": "CUDA events around every step, summed", "sharding": "independent sequences per rank, no collective"},
+                       "timing": "CUDA events around every step, summed", "sharding": "independent sequences per rank, no collective",
+                       **extra},
             "roofline": {"bound": "hbm", "kernel": wl["kernel"], "achieved": round(bwd_gbs, 1), "peak": peak, "unit": "GB/s",
                          "frac": round(bwd_gbs / peak, 4), "traffic": None, "peak_source": peak_src,
                          "algorithmic_bytes_per_launch": wl["bwd_bytes"], "ms_per_launch": round(bwd_ms, 4),
@@ -700,7 +770,7 @@ def main():
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
-    ap.add_argument("--workload", choices=["C1", "C2", "C3", "C4", "C5"], default="C2")
+    ap.add_argument("--workload", choices=["C1", "C2", "C3", "C4", "C5", "G"], default="C2")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
     ap.add_argument("--kernel-only", action="store_true",
                     help="device-resident timing only (no end-to-end or CPU leg): the command profiled under ncu")

@@ -116,6 +116,20 @@ int b200_gblock_fwd(int64_t B, int64_t L, int64_t I, int64_t O, int64_t na, int6
                     const void* ub, const void* taps, const void* a, const void* x0, void* y, void* y_pairs,
                     void* x_last, void* stream);
 
+/* Adjoint of b200_gblock_fwd for an upstream gradient gy [B,O,L] on y (same layouts, nb padded the
+ * same way): the all-pole adjoint of every pair (reading gy and the [O,I,na] coefficients in
+ * place through a row map, so the [B,I*O,L] broadcast of gy is never built) followed by the
+ * numerator adjoint.  Replaces what autograd runs for dynonet/core.py:214-250: the backward of
+ * sum/view, tsfast::dynonet_allpole_bwd (allpole_triton.py:174-213) and the grouped conv1d
+ * gradients.  Writes gub [B*I,pitch] (gradient w.r.t. the rows of ub: carried tail, then input),
+ * gtaps [B,O,I,nb] and ga [B,I*O,na] (per batch row; the caller sums over B), gx0 [B,I*O,na] when
+ * x0 != NULL.  The workspace holds the numerator-output gradient [B,I*O,L]. */
+size_t b200_gblock_bwd_workspace_bytes(int64_t B, int64_t L, int64_t I, int64_t O);
+int b200_gblock_bwd(int64_t B, int64_t L, int64_t I, int64_t O, int64_t na, int64_t nb, int64_t pitch,
+                    const void* gy, const void* ub, const void* taps, const void* a, const void* y_pairs,
+                    const void* x0, void* gub, void* gtaps, void* ga, void* gx0, void* workspace,
+                    size_t workspace_bytes, void* stream);
+
 /* ---- S3: fused Mamba selective-scan section ---------------------------------------------
  * delta = softplus(draw) (threshold 20); h_t = exp(delta_t A) h_{t-1} + delta_t u_t B_t;
  * out_t = (h_t . C_t + Dp u_t) * z_t * sigmoid(z_t); hlast = h_L.  All float32.

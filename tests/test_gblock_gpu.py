@@ -108,6 +108,37 @@ def test_chunked_rollout_equals_full_sequence():
     assert rel_err(torch.cat(parts, 1).cpu().numpy(), full.cpu().numpy()) < 1e-5
 
 
+def test_gradient_through_the_new_state():
+    """A loss on the returned filter state as well: the general adjoint against the reference's
+    formulation (grouped conv1d, all-pole op, slices) differentiated by autograd."""
+    import torch.nn.functional as F
+
+    from tsfast_b200 import allpole_b200, dynonet_b200 as dn
+
+    torch.manual_seed(1)
+    Bsz, L, I, O, nb, na = 2, 300, 2, 3, 8, 3
+    mk = lambda *s: torch.randn(*s, device="cuda")
+    u0, b0, a0 = mk(Bsz, L, I), mk(O, I, nb) * 0.3, mk(O, I, na) * 0.15
+    tail0, x00, gy, gx = mk(Bsz, nb - 1, I), mk(Bsz, I * O, na), mk(Bsz, L, O), mk(Bsz, I * O, na)
+
+    def grads(fused):
+        u, b, a, tail, x0 = (t.clone().requires_grad_() for t in (u0, b0, a0, tail0, x00))
+        if fused:
+            y, st = dn.linear_block(u, b, a, {"u": tail, "x": x0})
+            xl = st["x"]
+        else:
+            P = I * O
+            w = F.conv1d(torch.cat((tail, u), 1).transpose(1, 2), b.permute(1, 0, 2).reshape(P, 1, nb).flip(-1), groups=I)
+            yp = allpole_b200.run(a.permute(1, 0, 2).reshape(P, na), w, x0)
+            y = yp.view(Bsz, I, O, L).sum(1).transpose(1, 2)
+            xl = yp[..., L - na :].flip(-1)
+        ((y * gy).sum() + (xl * gx).sum()).backward()
+        return [t.grad.cpu().numpy() for t in (u, b, a, tail, x0)]
+
+    for got, ref, name in zip(grads(True), grads(False), ("gu", "gb", "ga", "gtail", "gx0")):
+        assert rel_err(got, ref) < 1e-4, name
+
+
 def test_module_mirror_loads_reference_state_dict_names():
     from tsfast_b200.dynonet_b200 import LinearDynamicalOperator
 

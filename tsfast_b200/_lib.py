@@ -40,6 +40,8 @@ SIGNATURES = {
     "b200_allpole_fwd": (_int, [_i64, _i64, _i64] + [_vp] * 5),
     "b200_allpole_bwd": (_int, [_i64, _i64, _i64] + [_vp] * 8),
     "b200_gblock_fwd": (_int, [_i64] * 7 + [_vp] * 8),
+    "b200_gblock_bwd_workspace_bytes": (_sz, [_i64] * 4),
+    "b200_gblock_bwd": (_int, [_i64] * 7 + [_vp] * 11 + [_sz, _vp]),
     "b200_mamba_chk_interval": (_int, []),
     "b200_mamba_fwd": (_int, [_i64] * 4 + [_vp] * 12),
     "b200_mamba_bwd_workspace_bytes": (_sz, [_i64] * 4),

@@ -44,6 +44,9 @@ struct AllpoleArgs {
     float* ga;         // bwd: [lanes, na]
     float* gy0;        // bwd: [lanes, na] or null
     long long lanes, L;
+    // bwd, G-block use: when gP > 0 (pairs per batch row, gO outputs), lane (b, pair = j*gO + i) reads its
+    // upstream gradient from row b*gO + i of `in` and its coefficients from row i*(gP/gO) + j of `a`
+    long long gP, gO;
 };
 
 // Steps per thread (SEG, a template parameter: 16 or 32), hence 32*SEG steps per warp tile; a
@@ -107,13 +110,16 @@ __global__ void __launch_bounds__(32 * W, MINB) allpole_kernel(const AllpoleArgs
 
     const long long L = p.L;
     const long long C = (L + kTile - 1) / kTile;
-    const float* in = p.in + lane * L;
+    const long long in_row = (BWD && p.gP > 0) ? (lane / p.gP) * p.gO + (lane % p.gP) % p.gO : lane;
+    const float* in = p.in + in_row * L;
     const float* yin = BWD ? p.yin + lane * L : nullptr;
     float* out = p.out + lane * L;
 
+    // with the G-block row map the coefficients are the block's [O, I, na] tensor: pair j*O + i -> (i, j)
+    const long long a_row = (BWD && p.gP > 0) ? ((lane % p.gP) % p.gO) * (p.gP / p.gO) + (lane % p.gP) / p.gO : lane;
     float a[NA];
 #pragma unroll
-    for (int j = 0; j < NA; ++j) a[j] = p.a[lane * NA + j];
+    for (int j = 0; j < NA; ++j) a[j] = p.a[a_row * NA + j];
 
     auto phys0_of = [&](long long c) -> long long { return BWD ? (L - (c + 1) * kTile) : c * kTile; };
     auto issue = [&](long long c, int slot) {
@@ -414,7 +420,8 @@ static int dispatch_na(int na, const AllpoleArgs& a, cudaStream_t st) {
 }
 
 static int run_allpole(bool bwd, long long lanes, long long L, long long na, const void* a, const void* in,
-                       const void* yin, const void* y0, void* out, void* ga, void* gy0, void* stream) {
+                       const void* yin, const void* y0, void* out, void* ga, void* gy0, void* stream,
+                       long long gP = 0, long long gO = 0) {
     if (lanes < 0 || L < 0 || na < 1) return B200_ERR_ARG;
     if (na > 16) return B200_ERR_UNSUPPORTED;
     if (lanes == 0) return B200_OK;
@@ -434,6 +441,7 @@ static int run_allpole(bool bwd, long long lanes, long long L, long long na, con
     p.gy0 = y0 ? static_cast<float*>(gy0) : nullptr;
     p.lanes = lanes;
     p.L = L;
+    p.gP = gP, p.gO = gO;
     const uintptr_t seq_or = (uintptr_t)in | (uintptr_t)yin | (uintptr_t)out;
     const bool vec = (L % 4 == 0) && (seq_or % 16 == 0);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -734,6 +742,216 @@ __global__ void __launch_bounds__(32 * W, 4) gblock_fwd_kernel(const GBlockArgs 
     cp_wait<0>();
 }
 
+// Adjoint of the G-block's numerator.  gw [B, I*O, L] is the gradient w.r.t. the numerator outputs
+// (what the all-pole adjoint produces); one warp owns (batch row b, input channel j), walks time in
+// 1024-step tiles and, inside a tile, the O pairs of its input:
+//   gub[b, j, NB-1 + t] = sum_i sum_k taps[i,j,k] gw[b, j*O+i, t + k]     (input gradient, tail included)
+//   gtaps[b, i, j, k]   = sum_t gw[b, j*O+i, t] ub[b, j, t + NB-1 - k]    (per batch row; summed by the caller)
+// The input tile is fetched once per tile, every gw tile once; per-thread tap sums live in shared
+// memory ([O][NB][32 lanes]) and are added in lane order at the end, so results are reproducible.
+struct GBlockBwdArgs {
+    const float* gw;    // [B, I*O, L]
+    const float* ub;    // [B*I, pitch]
+    const float* taps;  // [O, I, NB]
+    float* gub;         // [B*I, pitch]
+    float* gtaps;       // [B, O, I, NB]
+    long long B, I, O, L, pitch;
+};
+
+template <int NB, int VEC, int W, int S>
+__global__ void __launch_bounds__(32 * W, 4) gblock_num_bwd_kernel(const GBlockBwdArgs p) {
+    constexpr int kSeg = 32, kTile = 32 * kSeg, kChunk = kSeg + 4, kStageF = 33 * kChunk;
+    constexpr int PIECES = kTile / VEC, PPC = kSeg / VEC, HALO = (NB - 1 + VEC - 1) / VEC, NU = kSeg + NB - 1;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int w = threadIdx.x >> 5, lid = threadIdx.x & 31;
+    const long long widx = (long long)blockIdx.x * W + w;
+    if (widx >= p.B * p.I) return;  // warps never synchronise with each other
+    const long long b = widx / p.I, j = widx - b * p.I;
+    const int O = (int)p.O;
+    const long long L = p.L, P = p.I * p.O;
+
+    const int fper = (S + 3) * kStageF + 32 * kChunk + O * NB * 32;
+    float* ring = reinterpret_cast<float*>(smem_raw) + (size_t)w * fper;  // [S] gw tiles
+    float* ubuf = ring + S * kStageF;                                       // [3] input tiles
+    float* gstage = ubuf + 3 * kStageF;                                     // [32][kChunk] output staging
+    float* gbs = gstage + 32 * kChunk;                                      // [O][NB][32]
+    // tap sums start at zero; the tiles too, so that what a short last tile leaves uncopied is finite
+    for (int e = lid; e < fper; e += 32) ring[e] = 0.f;
+    __syncwarp();
+
+    const long long C = (L + kTile - 1) / kTile;
+    const long long items = C * O;  // item q = (tile q / O, output channel q % O)
+    auto copy_tile = [&](float* dst, const float* src, long long room) {
+#pragma unroll
+        for (int r = 0; r < PIECES / 32; ++r) {
+            const int gidx = r * 32 + lid;
+            if ((long long)gidx * VEC < room) {
+                float* d = dst + (gidx / PPC) * kChunk + (gidx % PPC) * VEC;
+                if constexpr (VEC == 4) cp_async16(d, src + gidx * VEC);
+                else cp_async4(d, src + gidx * VEC);
+            }
+        }
+        if (lid < HALO && (long long)(kTile + lid * VEC) < room) {
+            float* d = dst + 32 * kChunk + lid * VEC;
+            if constexpr (VEC == 4) cp_async16(d, src + kTile + lid * VEC);
+            else cp_async4(d, src + kTile + lid * VEC);
+        }
+    };
+    auto issue = [&](long long q, int slot) {
+        const long long c = q / O, i = q - c * O;
+        // gw rows are L long (L % 4 == 0 when VEC == 4): whole pieces only below L
+        copy_tile(ring + slot * kStageF, p.gw + (b * P + j * p.O + i) * L + c * kTile, L - c * kTile);
+        if (i == 0) copy_tile(ubuf + (int)(c % 3) * kStageF, p.ub + (b * p.I + j) * p.pitch + c * kTile, p.pitch - c * kTile);
+    };
+#pragma unroll
+    for (int q = 0; q < S - 1; ++q) {
+        if (q < items) issue(q, q);
+        cp_commit();
+    }
+
+    // gradient of the carried tail: gub[s] for s < NB-1 gathers gw[s - (NB-1) + k], k >= NB-1-s
+    if (lid < NB - 1) {
+        float acc = 0.f;
+        for (int i = 0; i < O; ++i) {
+            const float* g = p.gw + (b * P + j * p.O + i) * L;
+            const float* bt = p.taps + ((long long)i * p.I + j) * NB;
+            for (int k = NB - 1 - lid; k < NB; ++k) {
+                const long long t = lid - (NB - 1) + k;
+                if (t < L) acc = fmaf(bt[k], g[t], acc);
+            }
+        }
+        p.gub[(b * p.I + j) * p.pitch + lid] = acc;
+    }
+
+    float* grow = p.gub + (b * p.I + j) * p.pitch + (NB - 1);
+    long long q = 0;
+    for (long long c = 0; c < C; ++c) {
+        const long long t0 = c * kTile, tbase = t0 + lid * kSeg;
+        float uc[NU], guacc[kSeg];
+#pragma unroll
+        for (int r = 0; r < kSeg; ++r) guacc[r] = 0.f;
+        for (int i = 0; i < O; ++i, ++q) {
+            float* stage = ring + (int)(q % S) * kStageF;
+            cp_wait<S - 2>();
+            __syncwarp();
+            if (i == 0) {  // this tile's input samples: own chunk and the first NB-1 of the next one
+                const float* ut = ubuf + (int)(c % 3) * kStageF;
+#pragma unroll
+                for (int r = 0; r < kSeg / 4; ++r) {
+                    const float4 t4 = *reinterpret_cast<const float4*>(ut + lid * kChunk + 4 * r);
+                    uc[4 * r] = t4.x, uc[4 * r + 1] = t4.y, uc[4 * r + 2] = t4.z, uc[4 * r + 3] = t4.w;
+                }
+#pragma unroll
+                for (int r = 0; r < (NB - 1 + 3) / 4; ++r) {
+                    const float4 t4 = *reinterpret_cast<const float4*>(ut + (lid + 1) * kChunk + 4 * r);
+                    const float t[4] = {t4.x, t4.y, t4.z, t4.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e)
+                        if (4 * r + e < NB - 1) uc[kSeg + 4 * r + e] = t[e];
+                }
+                if (tbase + NU > L + NB - 1) {  // past the row: leftovers of an earlier tile
+#pragma unroll
+                    for (int r = 0; r < NU; ++r)
+                        if (tbase + r >= L + NB - 1) uc[r] = 0.f;
+                }
+            }
+            float gc[NU];  // gw[tbase .. tbase + 32 + NB-1), zero past the sequence
+#pragma unroll
+            for (int r = 0; r < kSeg / 4; ++r) {
+                const float4 t4 = *reinterpret_cast<const float4*>(stage + lid * kChunk + 4 * r);
+                gc[4 * r] = t4.x, gc[4 * r + 1] = t4.y, gc[4 * r + 2] = t4.z, gc[4 * r + 3] = t4.w;
+            }
+#pragma unroll
+            for (int r = 0; r < (NB - 1 + 3) / 4; ++r) {
+                const float4 t4 = *reinterpret_cast<const float4*>(stage + (lid + 1) * kChunk + 4 * r);
+                const float t[4] = {t4.x, t4.y, t4.z, t4.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    if (4 * r + e < NB - 1) gc[kSeg + 4 * r + e] = t[e];
+            }
+            if (tbase + NU > L) {
+#pragma unroll
+                for (int r = 0; r < NU; ++r)
+                    if (tbase + r >= L) gc[r] = 0.f;
+            }
+            __syncwarp();  // everyone has read this stage before the next item's copies may land
+            if (q + S - 1 < items) issue(q + S - 1, (int)((q + S - 1) % S));
+            cp_commit();
+
+            float bt[NB];
+#pragma unroll
+            for (int k = 0; k < NB; ++k) bt[k] = p.taps[((long long)i * p.I + j) * NB + k];
+#pragma unroll
+            for (int r = 0; r < kSeg; ++r) {
+                float acc = guacc[r];
+#pragma unroll
+                for (int k = 0; k < NB; ++k) acc = fmaf(bt[k], gc[r + k], acc);
+                guacc[r] = acc;
+            }
+            float* gb = gbs + (i * NB) * 32 + lid;
+#pragma unroll
+            for (int k = 0; k < NB; ++k) {
+                float acc = 0.f;
+#pragma unroll
+                for (int r = 0; r < kSeg; ++r) acc = fmaf(gc[r], uc[r + NB - 1 - k], acc);
+                gb[k * 32] += acc;
+            }
+        }
+        // the input gradient of this tile: staged, then stored as coalesced 4-byte rows (its
+        // position NB-1 + t in the row is not 16-byte aligned)
+#pragma unroll
+        for (int r = 0; r < kSeg / 4; ++r)
+            *reinterpret_cast<float4*>(gstage + lid * kChunk + 4 * r) =
+                make_float4(guacc[4 * r], guacc[4 * r + 1], guacc[4 * r + 2], guacc[4 * r + 3]);
+        __syncwarp();
+#pragma unroll 8
+        for (int r = 0; r < kSeg; ++r) {
+            const int x = r * 32 + lid;
+            if (t0 + x < L) __stcs(grow + t0 + x, gstage[(x / kSeg) * kChunk + (x % kSeg)]);
+        }
+        __syncwarp();
+    }
+    cp_wait<0>();
+    __syncwarp();
+    for (int e = lid; e < O * NB; e += 32) {  // e = i*NB + k: add the 32 lane sums in lane order
+        float acc = 0.f;
+        for (int l = 0; l < 32; ++l) acc += gbs[e * 32 + l];
+        const int i = e / NB, k = e - i * NB;
+        p.gtaps[((b * p.O + i) * p.I + j) * NB + k] = acc;
+    }
+}
+
+template <int NB, int VEC>
+static int launch_gblock_num_bwd(const GBlockBwdArgs& a, cudaStream_t st) {
+    constexpr int W = 2, S = 3;
+    const size_t fper = (size_t)(S + 3) * 33 * 36 + 32 * 36 + (size_t)a.O * NB * 32;
+    const size_t smem = W * fper * sizeof(float);
+    if (smem > 200 * 1024) return B200_ERR_UNSUPPORTED;
+    auto kern = gblock_num_bwd_kernel<NB, VEC, W, S>;
+    static size_t configured[64] = {0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && configured[dev] < smem) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return B200_ERR_LAUNCH;
+        configured[dev] = smem;
+    }
+    const long long grid = (a.B * a.I + W - 1) / W;
+    if (grid > 0x7fffffffLL) return B200_ERR_UNSUPPORTED;
+    kern<<<(unsigned int)grid, 32 * W, smem, st>>>(a);
+    return cudaGetLastError() == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
+}
+
+template <int VEC>
+static int dispatch_gblock_num_bwd(int nb, const GBlockBwdArgs& a, cudaStream_t st) {
+    switch (nb) {
+        case 4: return launch_gblock_num_bwd<4, VEC>(a, st);
+        case 8: return launch_gblock_num_bwd<8, VEC>(a, st);
+        case 16: return launch_gblock_num_bwd<16, VEC>(a, st);
+        default: return B200_ERR_UNSUPPORTED;
+    }
+}
+
 #ifndef GBLOCK_W
 #define GBLOCK_W 2  // (batch row, output channel) warps per CTA
 #endif
@@ -829,6 +1047,50 @@ int b200_allpole_fwd(int64_t lanes, int64_t L, int64_t na, const void* a, const 
 int b200_allpole_bwd(int64_t lanes, int64_t L, int64_t na, const void* g, const void* a, const void* y,
                      const void* y0, void* ga, void* gw, void* gy0, void* stream) {
     return b200::run_allpole(true, lanes, L, na, a, g, y, y0, gw, ga, gy0, stream);
+}
+
+size_t b200_gblock_bwd_workspace_bytes(int64_t B, int64_t L, int64_t I, int64_t O) {
+    if (B <= 0 || L <= 0 || I <= 0 || O <= 0) return 256;
+    return b200::align_up((size_t)B * I * O * L * sizeof(float), 256);
+}
+
+int b200_gblock_bwd(int64_t B, int64_t L, int64_t I, int64_t O, int64_t na, int64_t nb, int64_t pitch,
+                    const void* gy, const void* ub, const void* taps, const void* a, const void* y_pairs,
+                    const void* x0, void* gub, void* gtaps, void* ga, void* gx0, void* workspace,
+                    size_t workspace_bytes, void* stream) {
+    using namespace b200;
+    if (B < 0 || L < 0 || I < 1 || O < 1 || na < 1 || nb < 1 || pitch < L + nb - 1) return B200_ERR_ARG;
+    if (na > 4 || (nb != 4 && nb != 8 && nb != 16)) return B200_ERR_UNSUPPORTED;
+    if (B == 0) return B200_OK;
+    if (!ub || !taps || !a || !gub || !gtaps || !ga || (x0 && !gx0)) return B200_ERR_ARG;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (L == 0) {  // nothing flows through an empty chunk: zero gradients, the state passes through
+        cudaError_t e = cudaMemsetAsync(gub, 0, (size_t)B * I * pitch * sizeof(float), st);
+        if (e == cudaSuccess) e = cudaMemsetAsync(gtaps, 0, (size_t)B * O * I * nb * sizeof(float), st);
+        if (e == cudaSuccess) e = cudaMemsetAsync(ga, 0, (size_t)B * I * O * na * sizeof(float), st);
+        if (e == cudaSuccess && gx0) e = cudaMemsetAsync(gx0, 0, (size_t)B * I * O * na * sizeof(float), st);
+        return e == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
+    }
+    if (!gy || !y_pairs) return B200_ERR_ARG;
+    if (!workspace || ((uintptr_t)workspace % 256) != 0 || workspace_bytes < b200_gblock_bwd_workspace_bytes(B, L, I, O))
+        return B200_ERR_WORKSPACE;
+    // 1. denominator adjoint on every pair, upstream gradient and coefficients read through the row map
+    int rc = run_allpole(true, B * I * O, L, na, a, gy, y_pairs, x0, workspace, ga, gx0, stream, I * O, O);
+    if (rc != B200_OK) return rc;
+    // 2. numerator adjoint
+    GBlockBwdArgs p;
+    p.gw = static_cast<const float*>(workspace);
+    p.ub = static_cast<const float*>(ub);
+    p.taps = static_cast<const float*>(taps);
+    p.gub = static_cast<float*>(gub);
+    p.gtaps = static_cast<float*>(gtaps);
+    p.B = B, p.I = I, p.O = O, p.L = L, p.pitch = pitch;
+    const uintptr_t por = (uintptr_t)ub | (uintptr_t)taps | (uintptr_t)gub | (uintptr_t)gtaps;
+    if (por % 4 != 0) return B200_ERR_ARG;
+    const bool vec = (L % 4 == 0) && (pitch % 4 == 0) && (((uintptr_t)ub | (uintptr_t)workspace) % 16 == 0);
+    // positions of a row past NB-1 + L are not written by the kernel
+    if (cudaMemsetAsync(gub, 0, (size_t)B * I * pitch * sizeof(float), st) != cudaSuccess) return B200_ERR_LAUNCH;
+    return vec ? dispatch_gblock_num_bwd<4>((int)nb, p, st) : dispatch_gblock_num_bwd<1>((int)nb, p, st);
 }
 
 }  // extern "C"

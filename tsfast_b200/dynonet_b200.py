@@ -8,8 +8,8 @@ never reaches memory and the per-pair outputs only when the adjoint will need th
 
 * :func:`linear_block` is the functional form: ``(u, b_coeff, a_coeff, state) -> (y, new_state)``
   with tsfast's tensor layouts and state dict (``{"u": FIR tail, "x": IIR states}``).  It is
-  differentiable: the adjoint runs ``b200_allpole_bwd`` on the saved per-pair outputs and PyTorch's
-  grouped-convolution gradients for the numerator.
+  differentiable: the adjoint is ``b200_gblock_bwd`` (the all-pole adjoint of every pair reading the
+  output gradient in place, then one kernel for the numerator's input and tap gradients).
 * :class:`LinearDynamicalOperator` mirrors the reference module (same constructor, parameter names
   and ``forward(u, state=None, return_state=False)``), so a tsfast state dict loads into it.
 
@@ -50,6 +50,21 @@ def _padded_nb(nb: int) -> int:
     return next(s for s in _NB_SIZES if s >= nb)
 
 
+def _rows_and_taps(u, tail, b_coeff, NB):
+    """The kernels' input rows ``[B, I, pitch]`` (zeros, the carried tail, then ``u[b, :, j]``) and
+    the taps zero-padded to ``NB``."""
+    B, L, I = u.shape
+    O, _, nb = b_coeff.shape
+    pitch = (L + NB - 1 + 3) // 4 * 4
+    ub = u.new_zeros(B, I, pitch)
+    if tail is not None and nb > 1:
+        ub[:, :, NB - nb : NB - 1] = tail.transpose(1, 2)
+    ub[:, :, NB - 1 : NB - 1 + L] = u.transpose(1, 2)
+    taps = b_coeff.new_zeros(O, I, NB)
+    taps[:, :, :nb] = b_coeff
+    return ub, taps, pitch
+
+
 @torch.library.custom_op("b200scan::dynonet_gblock", mutates_args=())
 def _gblock_op(u: torch.Tensor, tail: torch.Tensor | None, b_coeff: torch.Tensor, a_coeff: torch.Tensor,
                x0: torch.Tensor | None, keep_pairs: bool) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
@@ -61,14 +76,7 @@ def _gblock_op(u: torch.Tensor, tail: torch.Tensor | None, b_coeff: torch.Tensor
     O, _, nb = b_coeff.shape
     na = a_coeff.shape[-1]
     NB = _padded_nb(nb)
-    pitch = (L + NB - 1 + 3) // 4 * 4
-    # rows (b, j): zeros, then the carried tail, then u[b, :, j]
-    ub = u.new_zeros(B, I, pitch)
-    if tail is not None and nb > 1:
-        ub[:, :, NB - nb : NB - 1] = tail.transpose(1, 2)
-    ub[:, :, NB - 1 : NB - 1 + L] = u.transpose(1, 2)
-    taps = b_coeff.new_zeros(O, I, NB)
-    taps[:, :, :nb] = b_coeff
+    ub, taps, pitch = _rows_and_taps(u, tail, b_coeff, NB)
     a_c = a_coeff.contiguous()
     x0_c = x0.contiguous() if x0 is not None else None
     _lib.require_dense_cuda(ub=ub, taps=taps, a=a_c, x0=x0_c)
@@ -91,10 +99,51 @@ def _(u, tail, b_coeff, a_coeff, x0, keep_pairs):
     return u.new_empty(B, O, L), yp, u.new_empty(B, I * O, na)
 
 
+@torch.library.custom_op("b200scan::dynonet_gblock_bwd", mutates_args=())
+def _gblock_bwd_op(gy: torch.Tensor, u: torch.Tensor, tail: torch.Tensor | None, b_coeff: torch.Tensor,
+                   a_coeff: torch.Tensor, x0: torch.Tensor | None, yp: torch.Tensor
+                   ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Gradients of ``sum(y * gy)``, gy [B,O,L]: ``(gu [B,L,I], gtail [B,nb-1,I], gb [O,I,nb],
+    ga [O,I,na], gx0 [B,I*O,na] or empty)``."""
+    B, L, I = u.shape
+    O, _, nb = b_coeff.shape
+    na = a_coeff.shape[-1]
+    NB = _padded_nb(nb)
+    ub, taps, pitch = _rows_and_taps(u, tail, b_coeff, NB)
+    gy_c, a_c, yp_c = gy.contiguous(), a_coeff.contiguous(), yp.contiguous()
+    x0_c = x0.contiguous() if x0 is not None else None
+    _lib.require_dense_cuda(gy=gy_c, ub=ub, taps=taps, a=a_c, x0=x0_c, y_pairs=yp_c)
+    gub = u.new_empty(B, I, pitch)
+    gtaps = u.new_empty(B, O, I, NB)
+    ga_l = u.new_empty(B, I * O, na)
+    gx0 = u.new_empty(B, I * O, na) if x0 is not None else None
+    if B:
+        nbytes = _lib.lib().b200_gblock_bwd_workspace_bytes(B, L, I, O)
+        ws = _lib.workspace(nbytes, u.device)
+        st = _lib.lib().b200_gblock_bwd(B, L, I, O, na, NB, pitch, _lib.ptr(gy_c), _lib.ptr(ub), _lib.ptr(taps),
+                                        _lib.ptr(a_c), _lib.ptr(yp_c), _lib.ptr(x0_c), _lib.ptr(gub), _lib.ptr(gtaps),
+                                        _lib.ptr(ga_l), _lib.ptr(gx0), _lib.ptr(ws), ws.numel(), _lib.stream_ptr(u.device))
+        _lib.check(st, "b200_gblock_bwd")
+    gu = gub[:, :, NB - 1 : NB - 1 + L].transpose(1, 2).clone(memory_format=torch.contiguous_format)
+    gtail = gub[:, :, NB - nb : NB - 1].transpose(1, 2).clone(memory_format=torch.contiguous_format)
+    gb = gtaps.sum(0)[:, :, :nb].clone(memory_format=torch.contiguous_format)
+    ga = ga_l.reshape(B, I, O, na).sum(0).permute(1, 0, 2).clone(memory_format=torch.contiguous_format)
+    return gu, gtail, gb, ga, (gx0 if gx0 is not None else u.new_empty(0))
+
+
+@_gblock_bwd_op.register_fake
+def _(gy, u, tail, b_coeff, a_coeff, x0, yp):
+    B, L, I = u.shape
+    nb = b_coeff.shape[-1]
+    gx0 = torch.empty_like(x0) if x0 is not None else u.new_empty(0)
+    return torch.empty_like(u), u.new_empty(B, nb - 1, I), torch.empty_like(b_coeff), torch.empty_like(a_coeff), gx0
+
+
 def _gblock_setup(ctx, inputs, output):
     u, tail, b_coeff, a_coeff, x0, keep_pairs = inputs
     _, yp, _ = output
     ctx.keep_pairs = keep_pairs
+    ctx.set_materialize_grads(False)
     ctx.save_for_backward(u, tail, b_coeff, a_coeff, x0, yp)
 
 
@@ -103,6 +152,19 @@ def _gblock_backward(ctx, gy, gyp, gxl):
     if not ctx.keep_pairs:
         raise RuntimeError("b200scan::dynonet_gblock was run without keeping the per-pair outputs; "
                            "call linear_block under autograd so that it keeps them")
+    B, L, I = u.shape
+    if gyp is None and gxl is None:  # the usual case: only y is used downstream
+        if gy is None:
+            gy = u.new_zeros(B, b_coeff.shape[0], L)
+        gu, gtail, gb, ga, gx0 = _gblock_bwd_op(gy, u, tail, b_coeff, a_coeff, x0, yp)
+        return gu, (gtail if tail is not None else None), gb, ga, (gx0 if x0 is not None else None), None
+    return _gblock_backward_general(u, tail, b_coeff, a_coeff, x0, yp, gy, gyp, gxl)
+
+
+def _gblock_backward_general(u, tail, b_coeff, a_coeff, x0, yp, gy, gyp, gxl):
+    """Gradients when the per-pair outputs or the new state are differentiated too: the per-pair
+    upstream gradient is built explicitly, then the all-pole adjoint and PyTorch's grouped
+    convolution gradients."""
     B, L, I = u.shape
     O, _, nb = b_coeff.shape
     na = a_coeff.shape[-1]
