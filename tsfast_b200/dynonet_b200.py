@@ -67,8 +67,10 @@ def _rows_and_taps(u, tail, b_coeff, NB):
 
 @torch.library.custom_op("b200scan::dynonet_gblock", mutates_args=())
 def _gblock_op(u: torch.Tensor, tail: torch.Tensor | None, b_coeff: torch.Tensor, a_coeff: torch.Tensor,
-               x0: torch.Tensor | None, keep_pairs: bool) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
-    """``(y [B,O,L], y_pairs [B,I*O,L] or empty, x_last [B,I*O,na])`` for u [B,L,I]."""
+               x0: torch.Tensor | None, keep_pairs: bool
+               ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    """``(y [B,O,L], y_pairs [B,I*O,L] or empty, x_last [B,I*O,na], rows, taps)`` for u [B,L,I]; the last
+    two are the kernel's input rows and padded taps, handed back so that the adjoint can reuse them."""
     why = supports(u, b_coeff, a_coeff)
     if why is not None:
         raise RuntimeError(f"b200scan::dynonet_gblock: {why}")
@@ -88,7 +90,7 @@ def _gblock_op(u: torch.Tensor, tail: torch.Tensor | None, b_coeff: torch.Tensor
                                         _lib.ptr(x0_c), _lib.ptr(y), _lib.ptr(yp) if keep_pairs else None,
                                         _lib.ptr(xl), _lib.stream_ptr(u.device))
         _lib.check(st, "b200_gblock_fwd")
-    return y, yp, xl
+    return y, yp, xl, ub, taps
 
 
 @_gblock_op.register_fake
@@ -96,20 +98,21 @@ def _(u, tail, b_coeff, a_coeff, x0, keep_pairs):
     B, L, I = u.shape
     O, na = b_coeff.shape[0], a_coeff.shape[-1]
     yp = u.new_empty(B, I * O, L) if keep_pairs else u.new_empty(0)
-    return u.new_empty(B, O, L), yp, u.new_empty(B, I * O, na)
+    NB = _padded_nb(b_coeff.shape[-1])
+    return (u.new_empty(B, O, L), yp, u.new_empty(B, I * O, na), u.new_empty(B, I, (L + NB - 1 + 3) // 4 * 4),
+            b_coeff.new_empty(O, I, NB))
 
 
 @torch.library.custom_op("b200scan::dynonet_gblock_bwd", mutates_args=())
-def _gblock_bwd_op(gy: torch.Tensor, u: torch.Tensor, tail: torch.Tensor | None, b_coeff: torch.Tensor,
-                   a_coeff: torch.Tensor, x0: torch.Tensor | None, yp: torch.Tensor
+def _gblock_bwd_op(gy: torch.Tensor, ub: torch.Tensor, taps: torch.Tensor, a_coeff: torch.Tensor,
+                   x0: torch.Tensor | None, yp: torch.Tensor, L: int, nb: int
                    ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
-    """Gradients of ``sum(y * gy)``, gy [B,O,L]: ``(gu [B,L,I], gtail [B,nb-1,I], gb [O,I,nb],
-    ga [O,I,na], gx0 [B,I*O,na] or empty)``."""
-    B, L, I = u.shape
-    O, _, nb = b_coeff.shape
+    """Gradients of ``sum(y * gy)``, gy [B,O,L], from the forward's rows and padded taps:
+    ``(gu [B,L,I], gtail [B,nb-1,I], gb [O,I,nb], ga [O,I,na], gx0 [B,I*O,na] or empty)``."""
+    u = ub
+    B, I, pitch = ub.shape
+    O, _, NB = taps.shape
     na = a_coeff.shape[-1]
-    NB = _padded_nb(nb)
-    ub, taps, pitch = _rows_and_taps(u, tail, b_coeff, NB)
     gy_c, a_c, yp_c = gy.contiguous(), a_coeff.contiguous(), yp.contiguous()
     x0_c = x0.contiguous() if x0 is not None else None
     _lib.require_dense_cuda(gy=gy_c, ub=ub, taps=taps, a=a_c, x0=x0_c, y_pairs=yp_c)
@@ -132,23 +135,23 @@ def _gblock_bwd_op(gy: torch.Tensor, u: torch.Tensor, tail: torch.Tensor | None,
 
 
 @_gblock_bwd_op.register_fake
-def _(gy, u, tail, b_coeff, a_coeff, x0, yp):
-    B, L, I = u.shape
-    nb = b_coeff.shape[-1]
-    gx0 = torch.empty_like(x0) if x0 is not None else u.new_empty(0)
-    return torch.empty_like(u), u.new_empty(B, nb - 1, I), torch.empty_like(b_coeff), torch.empty_like(a_coeff), gx0
+def _(gy, ub, taps, a_coeff, x0, yp, L, nb):
+    B, I, _ = ub.shape
+    O = taps.shape[0]
+    gx0 = torch.empty_like(x0) if x0 is not None else ub.new_empty(0)
+    return ub.new_empty(B, L, I), ub.new_empty(B, nb - 1, I), taps.new_empty(O, I, nb), torch.empty_like(a_coeff), gx0
 
 
 def _gblock_setup(ctx, inputs, output):
     u, tail, b_coeff, a_coeff, x0, keep_pairs = inputs
-    _, yp, _ = output
+    _, yp, _, ub, taps = output
     ctx.keep_pairs = keep_pairs
     ctx.set_materialize_grads(False)
-    ctx.save_for_backward(u, tail, b_coeff, a_coeff, x0, yp)
+    ctx.save_for_backward(u, tail, b_coeff, a_coeff, x0, yp, ub, taps)
 
 
-def _gblock_backward(ctx, gy, gyp, gxl):
-    u, tail, b_coeff, a_coeff, x0, yp = ctx.saved_tensors
+def _gblock_backward(ctx, gy, gyp, gxl, gub_unused, gtaps_unused):
+    u, tail, b_coeff, a_coeff, x0, yp, ub, taps = ctx.saved_tensors
     if not ctx.keep_pairs:
         raise RuntimeError("b200scan::dynonet_gblock was run without keeping the per-pair outputs; "
                            "call linear_block under autograd so that it keeps them")
@@ -156,7 +159,7 @@ def _gblock_backward(ctx, gy, gyp, gxl):
     if gyp is None and gxl is None:  # the usual case: only y is used downstream
         if gy is None:
             gy = u.new_zeros(B, b_coeff.shape[0], L)
-        gu, gtail, gb, ga, gx0 = _gblock_bwd_op(gy, u, tail, b_coeff, a_coeff, x0, yp)
+        gu, gtail, gb, ga, gx0 = _gblock_bwd_op(gy, ub, taps, a_coeff, x0, yp, L, b_coeff.shape[-1])
         return gu, (gtail if tail is not None else None), gb, ga, (gx0 if x0 is not None else None), None
     return _gblock_backward_general(u, tail, b_coeff, a_coeff, x0, yp, gy, gyp, gxl)
 
@@ -225,7 +228,7 @@ def linear_block(u: torch.Tensor, b_coeff: torch.Tensor, a_coeff: torch.Tensor, 
     nb = b_coeff.shape[-1]
     keep = torch.is_grad_enabled() and any(
         t is not None and t.requires_grad for t in (u, tail, b_coeff, a_coeff, x0))
-    y, _, x_last = _gblock_op(u, tail, b_coeff, a_coeff, x0, keep)
+    y, _, x_last, _, _ = _gblock_op(u, tail, b_coeff, a_coeff, x0, keep)
     B, L, I = u.shape
     if nb > 1:
         ubuf = torch.cat((tail if tail is not None else u.new_zeros(B, nb - 1, I), u[:, max(0, L - (nb - 1)) :]), dim=1)
