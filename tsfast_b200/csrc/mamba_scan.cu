@@ -115,15 +115,22 @@ __device__ __forceinline__ void copy_tile(float* dst, int ld, const float* src, 
     }
 }
 
+// Row pitch of the forward's [t][d] shared-memory tiles.  After a channel group's reduce-scatter
+// lane `ng` of a channel works on step tg + ng, so the TPC lanes of a channel touch TPC consecutive
+// rows at the same column; a pitch of 32/TPC (mod 32) words spreads those rows over distinct banks
+// (the pad stays a multiple of 4 floats so that rows remain 16-byte copyable).
+__host__ __device__ constexpr int mamba_ldd(int tpc, int db) { return tpc == 1 ? db : db + (32 / tpc > 4 ? 32 / tpc : 4); }
+
 // ================================================================================ forward
 template <int TPC, int DB, bool STORE_CHK, int VEC, int S>
 __global__ void __launch_bounds__(DB* TPC) mamba_fwd_kernel(const MambaArgs p) {
     constexpr int NTHR = DB * TPC;
     constexpr int NPAD = kNPT * TPC;
-    constexpr int STAGE = 3 * kT * DB + 2 * kT * NPAD;  // floats per ring stage
+    constexpr int LDD = mamba_ldd(TPC, DB);             // row pitch of the [t][d] tiles
+    constexpr int STAGE = 3 * kT * LDD + 2 * kT * NPAD;  // floats per ring stage
     extern __shared__ __align__(16) float smem[];
     float* ring = smem;                  // [S][STAGE]
-    float* outbuf = smem + S * STAGE;    // [2][kT][DB]
+    float* outbuf = smem + S * STAGE;    // [2][kT][LDD]
 
     const int tid = threadIdx.x;
     const int dl = tid / TPC, ng = tid % TPC;
@@ -135,7 +142,7 @@ __global__ void __launch_bounds__(DB* TPC) mamba_fwd_kernel(const MambaArgs p) {
     const bool d_ok = d < D;
     const int dcols = (int)((D - d0) < DB ? (D - d0) : DB);
 
-    for (int e = tid; e < S * STAGE + 2 * kT * DB; e += NTHR) smem[e] = 0.f;  // pads must read as zero
+    for (int e = tid; e < S * STAGE + 2 * kT * LDD; e += NTHR) smem[e] = 0.f;  // pads must read as zero
     __syncthreads();
 
     // Whole tiles of a CTA whose rows are whole 16-byte pieces take a path with no index
@@ -145,7 +152,7 @@ __global__ void __launch_bounds__(DB* TPC) mamba_fwd_kernel(const MambaArgs p) {
     constexpr int PPR4 = DB / 4;                                // 16-byte pieces per [t][d] row
     constexpr int TD_PIECES = kT * PPR4, N_PIECES = kT * TPC;   // per tensor and tile
     constexpr int TD_PER = (TD_PIECES + NTHR - 1) / NTHR, N_PER = (N_PIECES + NTHR - 1) / NTHR;
-    const int soff0 = (tid / PPR4) * DB + (tid % PPR4) * 4;
+    const int soff0 = (tid / PPR4) * LDD + (tid % PPR4) * 4;
     const long long goff0 = (long long)(tid / PPR4) * D + (tid % PPR4) * 4;
     const int soffn0 = (tid / TPC) * NPAD + (tid % TPC) * 4;
     const long long goffn0 = (long long)(tid / TPC) * N + (tid % TPC) * 4;
@@ -161,17 +168,17 @@ __global__ void __launch_bounds__(DB* TPC) mamba_fwd_kernel(const MambaArgs p) {
             for (int j = 0; j < TD_PER; ++j) {
                 if (TD_PIECES % NTHR == 0 || tid + j * NTHR < TD_PIECES) {
                     const long long g = ioff + goff0 + (long long)j * (4 * TPC) * D;
-                    float* sd = st + soff0 + j * (4 * TPC) * DB;
+                    float* sd = st + soff0 + j * (4 * TPC) * LDD;
                     mcp16(sd, p.draw + g);
-                    mcp16(sd + kT * DB, p.u + g);
-                    mcp16(sd + 2 * kT * DB, p.z + g);
+                    mcp16(sd + kT * LDD, p.u + g);
+                    mcp16(sd + 2 * kT * LDD, p.z + g);
                 }
             }
 #pragma unroll
             for (int j = 0; j < N_PER; ++j) {
                 if (N_PIECES % NTHR == 0 || tid + j * NTHR < N_PIECES) {
                     const long long g = ioffn + goffn0 + (long long)j * DB * N;
-                    float* sd = st + 3 * kT * DB + soffn0 + j * DB * NPAD;
+                    float* sd = st + 3 * kT * LDD + soffn0 + j * DB * NPAD;
                     mcp16(sd, p.Bt + g);
                     mcp16(sd + kT * NPAD, p.Ct + g);
                 }
@@ -181,23 +188,23 @@ __global__ void __launch_bounds__(DB* TPC) mamba_fwd_kernel(const MambaArgs p) {
         }
         ioff += kT * D, ioffn += kT * N;
         const long long off = (b * L + t0) * D + d0;
-        copy_tile<VEC, NTHR>(st, DB, p.draw + off, D, rows, DB, dcols, tid);
-        copy_tile<VEC, NTHR>(st + kT * DB, DB, p.u + off, D, rows, DB, dcols, tid);
-        copy_tile<VEC, NTHR>(st + 2 * kT * DB, DB, p.z + off, D, rows, DB, dcols, tid);
+        copy_tile<VEC, NTHR>(st, LDD, p.draw + off, D, rows, DB, dcols, tid);
+        copy_tile<VEC, NTHR>(st + kT * LDD, LDD, p.u + off, D, rows, DB, dcols, tid);
+        copy_tile<VEC, NTHR>(st + 2 * kT * LDD, LDD, p.z + off, D, rows, DB, dcols, tid);
         const long long offn = (b * L + t0) * N;
-        copy_tile<VEC, NTHR>(st + 3 * kT * DB, NPAD, p.Bt + offn, N, rows, NPAD, (int)N, tid);
-        copy_tile<VEC, NTHR>(st + 3 * kT * DB + kT * NPAD, NPAD, p.Ct + offn, N, rows, NPAD, (int)N, tid);
+        copy_tile<VEC, NTHR>(st + 3 * kT * LDD, NPAD, p.Bt + offn, N, rows, NPAD, (int)N, tid);
+        copy_tile<VEC, NTHR>(st + 3 * kT * LDD + kT * NPAD, NPAD, p.Ct + offn, N, rows, NPAD, (int)N, tid);
     };
     auto store_out = [&](long long c) {  // staged gated outputs of tile c -> global, coalesced
         const long long t0 = c * kT;
         const int rows = (int)((L - t0) < kT ? (L - t0) : kT);
-        const float* ob = outbuf + (c & 1) * kT * DB;
+        const float* ob = outbuf + (c & 1) * kT * LDD;
         if (fastc && rows == kT) {
 #pragma unroll
             for (int j = 0; j < TD_PER; ++j) {
                 if (TD_PIECES % NTHR == 0 || tid + j * NTHR < TD_PIECES) {
                     __stcs(reinterpret_cast<float4*>(p.out + ooff + goff0 + (long long)j * (4 * TPC) * D),
-                           *reinterpret_cast<const float4*>(ob + soff0 + j * (4 * TPC) * DB));
+                           *reinterpret_cast<const float4*>(ob + soff0 + j * (4 * TPC) * LDD));
                 }
             }
             ooff += kT * D;
@@ -210,9 +217,9 @@ __global__ void __launch_bounds__(DB* TPC) mamba_fwd_kernel(const MambaArgs p) {
             const int r = e / PPR, cc = (e - r * PPR) * VEC;
             if (cc < dcols) {
                 if constexpr (VEC == 4) {
-                    __stcs(reinterpret_cast<float4*>(dst + r * D + cc), *reinterpret_cast<const float4*>(ob + r * DB + cc));
+                    __stcs(reinterpret_cast<float4*>(dst + r * D + cc), *reinterpret_cast<const float4*>(ob + r * LDD + cc));
                 } else {
-                    __stcs(dst + r * D + cc, ob[r * DB + cc]);
+                    __stcs(dst + r * D + cc, ob[r * LDD + cc]);
                 }
             }
         }
@@ -250,27 +257,29 @@ __global__ void __launch_bounds__(DB* TPC) mamba_fwd_kernel(const MambaArgs p) {
             for (int j = 0; j < (kT * DB + NTHR - 1) / NTHR; ++j) {
                 const int e = tid + j * NTHR;
                 if ((kT * DB) % NTHR == 0 || e < kT * DB) {
-                    st[e] = softplus_f(st[e]);
-                    const float zz = st[2 * kT * DB + e];
-                    st[2 * kT * DB + e] = zz * sigmoid_f(zz);
+                    const int o = (e / DB) * LDD + (e % DB);
+                    st[o] = softplus_f(st[o]);
+                    const float zz = st[2 * kT * LDD + o];
+                    st[2 * kT * LDD + o] = zz * sigmoid_f(zz);
                 }
             }
         } else {
             for (int e = tid; e < tlive * DB; e += NTHR) {
-                st[e] = softplus_f(st[e]);
-                const float zz = st[2 * kT * DB + e];
-                st[2 * kT * DB + e] = zz * sigmoid_f(zz);
+                const int o = (e / DB) * LDD + (e % DB);
+                st[o] = softplus_f(st[o]);
+                const float zz = st[2 * kT * LDD + o];
+                st[2 * kT * LDD + o] = zz * sigmoid_f(zz);
             }
         }
         __syncthreads();
 
-        float* ob = outbuf + (c & 1) * kT * DB;
-        const float* Bs = st + 3 * kT * DB + n0;
+        float* ob = outbuf + (c & 1) * kT * LDD;
+        const float* Bs = st + 3 * kT * LDD + n0;
         const float* Cs = Bs + kT * NPAD;
         // one time step of this thread's 4 states; returns its share of y_t = h_t . C_t
         auto state_step = [&](int t) -> float {
-            const float delta = st[t * DB + dl];
-            const float du = delta * st[kT * DB + t * DB + dl];
+            const float delta = st[t * LDD + dl];
+            const float du = delta * st[kT * LDD + t * LDD + dl];
             const float4 Bv = *reinterpret_cast<const float4*>(Bs + t * NPAD);
             const float4 Cv = *reinterpret_cast<const float4*>(Cs + t * NPAD);
             const float bq[kNPT] = {Bv.x, Bv.y, Bv.z, Bv.w}, cq[kNPT] = {Cv.x, Cv.y, Cv.z, Cv.w};
@@ -286,7 +295,7 @@ __global__ void __launch_bounds__(DB* TPC) mamba_fwd_kernel(const MambaArgs p) {
         // gated output of step t for this thread's channel (kept in a register until the tile is
         // done: a shared-memory store inside the loop would pin every later load behind it)
         auto gated = [&](int t, float y) -> float {
-            return (y + Dp * st[kT * DB + t * DB + dl]) * st[2 * kT * DB + t * DB + dl];
+            return (y + Dp * st[kT * LDD + t * LDD + dl]) * st[2 * kT * LDD + t * LDD + dl];
         };
         constexpr int G = (TPC >= 2 && TPC <= kT) ? TPC : 1;  // steps whose y sums are reduced together
         auto store_chk = [&](int t_done) {  // state after step t_done (tile-local) -> its checkpoint slot
@@ -317,8 +326,8 @@ __global__ void __launch_bounds__(DB* TPC) mamba_fwd_kernel(const MambaArgs p) {
 #pragma unroll
                 for (int k = 0; k < G; ++k) {
                     const int t = tg + k;
-                    const float delta = st[t * DB + dl];
-                    const float du = delta * st[kT * DB + t * DB + dl];
+                    const float delta = st[t * LDD + dl];
+                    const float du = delta * st[kT * LDD + t * LDD + dl];
                     const float4 Bv = *reinterpret_cast<const float4*>(Bs + t * NPAD);
                     const float4 Cv = *reinterpret_cast<const float4*>(Cs + t * NPAD);
                     cc[k][0] = make_float2(Cv.x, Cv.y), cc[k][1] = make_float2(Cv.z, Cv.w);
@@ -353,7 +362,7 @@ __global__ void __launch_bounds__(DB* TPC) mamba_fwd_kernel(const MambaArgs p) {
             h[0] = hp[0].x, h[1] = hp[0].y, h[2] = hp[1].x, h[3] = hp[1].y;
 #pragma unroll
             for (int j = 0; j < kT / G; ++j) {
-                if (G > 1 || ng == 0) ob[(j * G + (G > 1 ? ng : 0)) * DB + dl] = yout[j];
+                if (G > 1 || ng == 0) ob[(j * G + (G > 1 ? ng : 0)) * LDD + dl] = yout[j];
             }
         } else {
             for (int t = 0; t < tlive; ++t) {
@@ -361,7 +370,7 @@ __global__ void __launch_bounds__(DB* TPC) mamba_fwd_kernel(const MambaArgs p) {
                 if ((t + 1) % kTB == 0) store_chk(t);
 #pragma unroll
                 for (int off = 1; off < TPC; off <<= 1) yp += __shfl_xor_sync(0xffffffffu, yp, off);
-                if (ng == 0) ob[t * DB + dl] = gated(t, yp);
+                if (ng == 0) ob[t * LDD + dl] = gated(t, yp);
             }
         }
     }
@@ -823,7 +832,8 @@ static int set_smem(K kern, size_t bytes, bool* configured) {
 template <int TPC, bool STORE_CHK, int VEC>
 static int launch_mamba_fwd(const MambaArgs& a, cudaStream_t st) {
     constexpr int DB = mamba_db(TPC), S = MAMBA_FWD_S, NTHR = DB * TPC;
-    constexpr size_t smem = sizeof(float) * ((size_t)S * (3 * kT * DB + 2 * kT * kNPT * TPC) + 2 * kT * DB);
+    constexpr int LDD = mamba_ldd(TPC, DB);
+    constexpr size_t smem = sizeof(float) * ((size_t)S * (3 * kT * LDD + 2 * kT * kNPT * TPC) + 2 * kT * LDD);
     auto kern = mamba_fwd_kernel<TPC, DB, STORE_CHK, VEC, S>;
     static bool configured[64] = {false};
     if (set_smem(kern, smem, configured) != B200_OK) return B200_ERR_LAUNCH;
