@@ -350,9 +350,35 @@ def make_gblock():
     print("gblock", len(names), "cases")
 
 
+def make_dynonet():
+    """A small reference DynoNet (tsfast/models/architectures/dynonet/core.py:257-346) in float64:
+    parameters, input, output, and the gradient of ``sum(y * g)`` w.r.t. every parameter."""
+    from tsfast.models.architectures.dynonet.core import DynoNet
+
+    torch.manual_seed(11)
+    net = DynoNet(2, 1, n_channels=4, nb=8, na=2, hidden_size=16, hidden_layers=1, bypass=True).double()
+    with torch.no_grad():
+        for n_, p_ in net.named_parameters():
+            if n_.endswith("a_coeff"):
+                p_.copy_((torch.randn(p_.shape) * 0.2).double())  # poles away from the origin; float32 values
+            else:
+                p_.copy_(p_.float().double())
+    gen = torch.Generator().manual_seed(12)
+    u = torch.randn(3, 700, 2, generator=gen)
+    g = torch.randn(3, 700, 1, generator=gen)
+    y = net(_to64(u))
+    (y * _to64(g)).sum().backward()
+    store = {"u": _np(u), "g": _np(g), "ref64_y": _np(y)}
+    for n_, p_ in net.named_parameters():
+        store[f"param_{n_}"] = _np(p_.float())
+        store[f"grad_{n_}"] = _np(p_.grad)
+    np.savez_compressed(HERE / "dynonet.npz", **store)
+    print("dynonet", len(list(net.named_parameters())), "parameters")
+
+
 if __name__ == "__main__":
     torch.set_num_threads(4)
-    which = sys.argv[1:] or ["diag", "sel", "mamba", "allpole", "lru", "conv", "gblock"]
+    which = sys.argv[1:] or ["diag", "sel", "mamba", "allpole", "lru", "conv", "gblock", "dynonet"]
     if "diag" in which:
         make_diag("diag")
     if "sel" in which:
@@ -367,3 +393,5 @@ if __name__ == "__main__":
         make_conv()
     if "gblock" in which:
         make_gblock()
+    if "dynonet" in which:
+        make_dynonet()

@@ -152,6 +152,27 @@ def test_module_mirror_loads_reference_state_dict_names():
     assert op.b_coeff.grad is not None and op.a_coeff.grad is not None
 
 
+def test_dynonet_matches_reference_model():
+    """The DynoNet mirror with the reference model's parameters (loaded by name) reproduces its
+    float64 output and parameter gradients (fixture from tsfast's DynoNet, dynonet/core.py:257-346)."""
+    from pathlib import Path
+
+    from tsfast_b200.dynonet_b200 import DynoNet
+
+    z = np.load(Path(__file__).parent / "golden" / "dynonet.npz")
+    net = DynoNet(2, 1, n_channels=4, nb=8, na=2, hidden_size=16, hidden_layers=1, bypass=True)
+    sd = {k[len("param_"):]: torch.from_numpy(z[k]) for k in z.files if k.startswith("param_")}
+    assert set(sd) == set(net.state_dict())
+    net.load_state_dict(sd)
+    net.cuda()
+    y = net(_dev(z["u"]))
+    (y * _dev(z["g"])).sum().backward()
+    torch.cuda.synchronize()
+    assert rel_err(_np(y), z["ref64_y"]) < REL
+    for name, p_ in net.named_parameters():
+        assert rel_err(_np(p_.grad), z["grad_" + name]) < 2e-4, name
+
+
 def test_unsupported_shapes_raise():
     from tsfast_b200 import dynonet_b200 as dn
 
