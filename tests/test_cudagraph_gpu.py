@@ -99,3 +99,31 @@ def test_graph_capture_of_mamba_and_allpole():
     torch.cuda.synchronize()
     for got, want in zip(captured, run()):
         assert torch.equal(got, want)
+
+
+def test_graph_capture_of_conv_and_dynonet_block():
+    from tsfast_b200 import conv_b200, dynonet_b200
+
+    torch.manual_seed(3)
+    r = lambda *s: torch.randn(*s, device="cuda")  # noqa: E731
+    x, tail, w, bias, gy = r(2, 90, 48), r(2, 48, 3), r(48, 4) * 0.5, r(48), r(2, 90, 48)
+    u, b, a = r(2, 1300, 2), r(3, 2, 8) * 0.3, r(3, 2, 2) * 0.2
+    st_u, st_x, gyb = r(2, 7, 2), r(2, 6, 2), r(2, 3, 1300)
+
+    def run():
+        y = conv_b200._conv_silu_op(x, tail, w, bias)
+        cg = conv_b200._conv_silu_bwd_op(gy, x, tail, w, bias)
+        yb, yp, xl, ub, taps = dynonet_b200._gblock_op(u, st_u, b, a, st_x, True)
+        bg = dynonet_b200._gblock_bwd_op(gyb, ub, taps, a, st_x, yp, u.shape[1], b.shape[-1])
+        return (y, *cg, yb, yp, xl, *bg)
+
+    run(), run()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        captured = run()
+    x.normal_(), u.normal_(), gyb.normal_()
+    graph.replay()
+    torch.cuda.synchronize()
+    for got, want in zip(captured, run()):
+        assert torch.equal(got, want)
