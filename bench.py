@@ -13,7 +13,7 @@ same metric through the public API from pinned HOST buffers with the host<->devi
 the timed region, `roofline` the dominant kernel (the adjoint) against the measured HBM peak, and
 `cpu_baseline` the CPU oracle (a C port of the reference's CPU kernels) on the host cores.
 `--impl reference` times that CPU port alone and prints the same line shape.
-`--workload C1|C3|C4|C5|G` measures the other configurations the same way (complex LRU scan, Mamba
+`--workload C1|C3|C4|C5|G|V` measures the other configurations the same way (complex LRU scan, Mamba
 section, all-pole filter, DeepLRU data-parallel training step); C2 is the headline.
 """
 
@@ -458,6 +458,35 @@ def _workload(name, torch, dev, rank):
                     h2d=2 * E, d2h=2 * E, dtype="f32", launches=2, kernel="allpole_kernel<NA=4, adjoint> (b200_allpole_bwd)",
                     fwd=lambda: allpole_b200._allpole_op(a, w, None), bwd=lambda o: allpole_b200._allpole_bwd_op(g, a, o, None),
                     e2e=e2e, cpu=cpu)
+    if name == "V":
+        from tsfast_b200 import conv_b200
+
+        Bn, L, D, K = 32, 2048, 512, 4
+        x, gy, tail = rn(Bn, L, D), rn(Bn, L, D), rn(Bn, D, K - 1)
+        w, bias = rn(D, K) * 0.5, rn(D)
+        E = Bn * L * D * 4
+        hx, hgy, hy, hgx = pin(x), pin(gy), pin(x), pin(x)
+
+        def e2e():
+            dx = hx.to(dev, non_blocking=True).requires_grad_()
+            ww, bb = w.clone().requires_grad_(), bias.clone().requires_grad_()
+            y = conv_b200.run(dx, tail, ww.unsqueeze(1), bb)
+            y.backward(hgy.to(dev, non_blocking=True))
+            hy.copy_(y.detach(), non_blocking=True)
+            hgx.copy_(dx.grad, non_blocking=True)
+            return ww.grad.cpu()
+
+        def cpu(rows):
+            from oracle import oracle as O_
+            x_, g_, t_ = x[:rows].cpu().numpy(), gy[:rows].cpu().numpy(), tail[:rows].cpu().numpy()
+            w_, b_ = w.cpu().numpy(), bias.cpu().numpy()
+            return lambda: (O_.conv_fwd(x_, t_, w_, b_), O_.conv_bwd(g_, x_, t_, w_, b_))
+
+        return dict(desc="V: Mamba causal depthwise conv (K=4) + SiLU fwd+bwd, B=32 T=2048 D=512 fp32 (the step feeding C3)",
+                    fwd_bytes=2 * E, bwd_bytes=3 * E, elems=2 * Bn * L * D, rows=Bn, sample_rows=8, flush=False,
+                    h2d=2 * E, d2h=2 * E, dtype="f32", launches=4, kernel="conv_silu_bwd_kernel<K=4> + partial sums (b200_conv_silu_bwd)",
+                    fwd=lambda: conv_b200._conv_silu_op(x, tail, w, bias),
+                    bwd=lambda o: conv_b200._conv_silu_bwd_op(gy, x, tail, w, bias), e2e=e2e, cpu=cpu)
     if name == "G":
         from tsfast_b200 import dynonet_b200
 
@@ -545,7 +574,7 @@ def run_workload(args):
     if args.workload == "C5":
         return _run_c5(args, torch, dist, dev, world, rank, local)
     wl = _workload(args.workload, torch, dev, rank)
-    flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if wl["flush"] else None
+    flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
 
     def barrier():
         if world > 1:
@@ -553,10 +582,12 @@ def run_workload(args):
         torch.cuda.synchronize()
 
     def timed(fn, n):
-        """Sum of per-call device times of fn() over n calls (L2 flushed before each when needed)."""
+        """Mean device time of fn() over n calls.  A 256 MB buffer is rewritten four times before
+        every call: that flushes L2 and keeps the GPU busy while the host enqueues fn(), so the
+        two events bracket the call's device work and not the host's launch path."""
         tot = 0.0
         for _ in range(n):
-            if flush_buf is not None:
+            for _ in range(4):
                 flush_buf.zero_()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
@@ -614,9 +645,9 @@ def run_workload(args):
             "scaling": "weak", "vs_baseline": None, "dtype": wl["dtype"], "data": "synthetic",
             "config": {"workload": wl["desc"], "algorithmic_bytes_per_step_per_gpu": step_bytes,
                        "state_elements_per_s": round(wl["elems"] * world / (ms * 1e-3)),
-                       "l2": ("working set fits in L2: a 256 MB buffer is rewritten before every timed call"
-                              if wl["flush"] else "streamed tensors are larger than the 126 MB L2; no flush needed"),
-                       "timing": "CUDA events around every step, summed", "sharding": "independent sequences per rank, no collective",
+                       "l2": ("working set fits in L2; " if wl["flush"] else "streamed tensors are larger than the 126 MB L2; ")
+                             + "a 256 MB buffer is rewritten before every timed call",
+                       "timing": "CUDA events around every step (enqueued behind an L2-flushing write so that host launch time is not inside), averaged", "sharding": "independent sequences per rank, no collective",
                        **extra},
             "roofline": {"bound": "hbm", "kernel": wl["kernel"], "achieved": round(bwd_gbs, 1), "peak": peak, "unit": "GB/s",
                          "frac": round(bwd_gbs / peak, 4), "traffic": None, "peak_source": peak_src,
@@ -770,7 +801,7 @@ def main():
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
-    ap.add_argument("--workload", choices=["C1", "C2", "C3", "C4", "C5", "G"], default="C2")
+    ap.add_argument("--workload", choices=["C1", "C2", "C3", "C4", "C5", "G", "V"], default="C2")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
     ap.add_argument("--kernel-only", action="store_true",
                     help="device-resident timing only (no end-to-end or CPU leg): the command profiled under ncu")
