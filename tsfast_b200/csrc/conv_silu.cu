@@ -15,6 +15,7 @@
 // gradients per thread; those are reduced over (batch, segment) through partial buffers added in
 // a fixed order, and the K-1 tail gradients come from the first segment.  No atomics.
 #include <initializer_list>
+#include <type_traits>
 
 #include "common.cuh"
 
@@ -28,13 +29,13 @@ constexpr int kConvThreads = 128;
 // Rows a thread loads per batch and the widest per-thread channel vector, per direction.  The
 // adjoint keeps about 25 registers per channel (weights, their gradients, two windows); 8-byte
 // vectors fit twice the CTAs per SM and measured faster than 16-byte ones in both directions
-// (B=32, L=2048, D=512, K=4: forward 4.4 -> 4.8 TB/s, adjoint 2.2 -> 3.4 TB/s together with the
-// prefetch of the next batch and the wider partial-sum kernel).
+// (B=32, L=2048, D=512, K=4: forward 4.4 -> 4.9 TB/s, adjoint 2.2 -> 3.8 TB/s together with the
+// prefetch of the next batch, the check-free interior path and the wider partial-sum kernel).
 #ifndef CONV_FWD_U
 #define CONV_FWD_U 8
 #endif
 #ifndef CONV_BWD_U
-#define CONV_BWD_U 2
+#define CONV_BWD_U 8
 #endif
 #ifndef CONV_FWD_PIPE
 #define CONV_FWD_PIPE 1  // request the next batch of rows before working on the current one
@@ -133,45 +134,63 @@ __global__ void __launch_bounds__(kConvThreads) conv_silu_fwd_kernel(const ConvA
 #pragma unroll
         for (int k = 0; k < K; ++k) wgt[k][q] = d_ok ? p.w[(d + q) * K + k] : 0.f;
     }
-    VecT<VEC> win[K - 1 > 0 ? K - 1 : 1];  // X(t-K+1) .. X(t-1)
+    // A segment whose rows (left context and prefetch included) all lie inside the sequence takes
+    // the same loop without range checks, tail lookups or per-row index arithmetic: this kernel is
+    // bound by instruction issue, not by memory, and the checks were half of its instructions.
+    static_assert(kSegT % kUnroll == 0, "whole batches per segment");
+    const bool interior = t0 >= K - 1 && t0 + kSegT + kUnroll <= p.L;
+    const float* xrow = p.x + b * p.sxb + d;   // row s of x at xrow + s * sxl
+    float* orow = p.out + b * p.L * p.D + d;   // row t of out at orow + t * D
+    auto body = [&](auto tag) {
+        constexpr bool IN = decltype(tag)::value;
+        auto row = [&](long long sidx, bool ok) -> VecT<VEC> {
+            if constexpr (IN) return ldv<VEC>(xrow + sidx * p.sxl);
+            else return load_x<K, VEC>(p, b, sidx, d, ok);
+        };
+        VecT<VEC> win[K - 1 > 0 ? K - 1 : 1];  // X(t-K+1) .. X(t-1)
 #pragma unroll
-    for (int i = 0; i < K - 1; ++i) win[i] = load_x<K, VEC>(p, b, t0 - (K - 1) + i, d, d_ok);
+        for (int i = 0; i < K - 1; ++i) win[i] = row(t0 - (K - 1) + i, d_ok);
 
-    // rows of the next batch are requested before the current batch is worked on
-    VecT<VEC> nxt[kUnroll];
-    if constexpr (CONV_FWD_PIPE) {
-#pragma unroll
-        for (int i = 0; i < kUnroll; ++i) nxt[i] = load_x<K, VEC>(p, b, t0 + i, d, d_ok && t0 + i < t1);
-    }
-    for (long long tb = t0; tb < t1; tb += kUnroll) {
-        VecT<VEC> cur[kUnroll];
+        // rows of the next batch are requested before the current batch is worked on
+        VecT<VEC> nxt[kUnroll];
         if constexpr (CONV_FWD_PIPE) {
 #pragma unroll
-            for (int i = 0; i < kUnroll; ++i) cur[i] = nxt[i];
-#pragma unroll
-            for (int i = 0; i < kUnroll; ++i)
-                nxt[i] = load_x<K, VEC>(p, b, tb + kUnroll + i, d, d_ok && tb + kUnroll + i < t1);
-        } else {
-#pragma unroll
-            for (int i = 0; i < kUnroll; ++i) cur[i] = load_x<K, VEC>(p, b, tb + i, d, d_ok && tb + i < t1);
+            for (int i = 0; i < kUnroll; ++i) nxt[i] = row(t0 + i, d_ok && t0 + i < t1);
         }
+        for (long long tb = t0; tb < t1; tb += kUnroll) {
+            VecT<VEC> cur[kUnroll];
+            if constexpr (CONV_FWD_PIPE) {
 #pragma unroll
-        for (int i = 0; i < kUnroll; ++i) {
-            if (tb + i < t1) {
-                VecT<VEC> o;
+                for (int i = 0; i < kUnroll; ++i) cur[i] = nxt[i];
 #pragma unroll
-                for (int q = 0; q < VEC; ++q) {
-                    float pre = fmaf(wgt[K - 1][q], cur[i].v[q], bs[q]);
+                for (int i = 0; i < kUnroll; ++i) nxt[i] = row(tb + kUnroll + i, d_ok && tb + kUnroll + i < t1);
+            } else {
 #pragma unroll
-                    for (int k = 0; k < K - 1; ++k) pre = fmaf(wgt[k][q], win[k].v[q], pre);
-                    o.v[q] = pre * sigmoid_fast(pre);
+                for (int i = 0; i < kUnroll; ++i) cur[i] = row(tb + i, d_ok && tb + i < t1);
+            }
+#pragma unroll
+            for (int i = 0; i < kUnroll; ++i) {
+                if (IN || tb + i < t1) {
+                    VecT<VEC> o;
+#pragma unroll
+                    for (int q = 0; q < VEC; ++q) {
+                        float pre = fmaf(wgt[K - 1][q], cur[i].v[q], bs[q]);
+#pragma unroll
+                        for (int k = 0; k < K - 1; ++k) pre = fmaf(wgt[k][q], win[k].v[q], pre);
+                        o.v[q] = pre * sigmoid_fast(pre);
+                    }
+                    if (IN || d_ok) stv<VEC>(orow + (tb + i) * p.D, o);
+#pragma unroll
+                    for (int k = 0; k + 1 < K - 1; ++k) win[k] = win[k + 1];
+                    if (K > 1) win[K - 2 > 0 ? K - 2 : 0] = cur[i];
                 }
-                if (d_ok) stv<VEC>(p.out + (b * p.L + tb + i) * p.D + d, o);
-#pragma unroll
-                for (int k = 0; k + 1 < K - 1; ++k) win[k] = win[k + 1];
-                if (K > 1) win[K - 2 > 0 ? K - 2 : 0] = cur[i];
             }
         }
+    };
+    if (interior) {
+        if (d_ok) body(std::true_type{});
+    } else {
+        body(std::false_type{});
     }
 }
 
@@ -201,9 +220,20 @@ __global__ void __launch_bounds__(kConvThreads) conv_silu_bwd_kernel(const ConvA
 #pragma unroll
         for (int k = 0; k < K - 1; ++k) gfirst[k][q] = 0.f;
     }
+    // Segments whose rows (context, the K-1 steps into the next segment and the prefetch) all lie
+    // inside the sequence run the same loop without range checks or per-row index arithmetic.
+    const bool interior = t0 >= K - 1 && t0 + kSegT + (K - 1) + 2 * kUnroll <= p.L;
+    const float* xrow = p.x + b * p.sxb + d;      // row s of x at xrow + s * sxl
+    const float* gyrow = p.gy + b * p.L * p.D + d;  // row t of gy / gx at + t * D
+    float* gxrow = p.gx + b * p.L * p.D + d;
+    auto body = [&](auto tag) {
+    constexpr bool IN = decltype(tag)::value;
     VecT<VEC> win[K];  // X(t-K+1) .. X(t)
 #pragma unroll
-    for (int i = 0; i < K - 1; ++i) win[i + 1] = load_x<K, VEC>(p, b, t0 - (K - 1) + i, d, d_ok);
+    for (int i = 0; i < K - 1; ++i) {
+        if constexpr (IN) win[i + 1] = ldv<VEC>(xrow + (t0 - (K - 1) + i) * p.sxl);
+        else win[i + 1] = load_x<K, VEC>(p, b, t0 - (K - 1) + i, d, d_ok);
+    }
 
     // rows of the next batch are requested before the current batch is worked on
     VecT<VEC> nx[kUnroll], ngy[kUnroll];
@@ -211,11 +241,16 @@ __global__ void __launch_bounds__(kConvThreads) conv_silu_bwd_kernel(const ConvA
 #pragma unroll
         for (int i = 0; i < kUnroll; ++i) {
             const long long t = tb + i;
-            const bool live = d_ok && t < tend && t < p.L;
-            nx[i] = load_x<K, VEC>(p, b, t, d, live);
+            if constexpr (IN) {
+                nx[i] = ldv<VEC>(xrow + t * p.sxl);
+                ngy[i] = ldv<VEC>(gyrow + t * p.D);
+            } else {
+                const bool live = d_ok && t < tend && t < p.L;
+                nx[i] = load_x<K, VEC>(p, b, t, d, live);
 #pragma unroll
-            for (int q = 0; q < VEC; ++q) ngy[i].v[q] = 0.f;
-            if (live) ngy[i] = ldv<VEC>(p.gy + (b * p.L + t) * p.D + d);
+                for (int q = 0; q < VEC; ++q) ngy[i].v[q] = 0.f;
+                if (live) ngy[i] = ldv<VEC>(gyrow + t * p.D);
+            }
         }
     };
     if constexpr (CONV_BWD_PIPE) fetch(t0);
@@ -232,7 +267,7 @@ __global__ void __launch_bounds__(kConvThreads) conv_silu_bwd_kernel(const ConvA
 #pragma unroll
                 for (int k = 0; k < K - 1; ++k) win[k] = win[k + 1];
                 win[K - 1] = cur[i];
-                const bool in_seq = t < p.L, own = t < t1;
+                const bool in_seq = IN || t < p.L, own = t < t1;
                 VecT<VEC> gxo;
 #pragma unroll
                 for (int q = 0; q < VEC; ++q) {
@@ -253,16 +288,22 @@ __global__ void __launch_bounds__(kConvThreads) conv_silu_bwd_kernel(const ConvA
 #pragma unroll
                     for (int k = 0; k < K; ++k) acc = fmaf(wgt[k][q], gwin[k][q], acc);
                     gxo.v[q] = acc;
-                    if (K > 1 && seg == 0) {
+                    if (!IN && K > 1 && seg == 0) {
 #pragma unroll
                         for (int k = 0; k < K - 1; ++k)
                             if (t == k) gfirst[k][q] = gp;
                     }
                 }
                 const long long s = t - (K - 1);
-                if (d_ok && s >= t0 && s < t1) stv<VEC>(p.gx + (b * p.L + s) * p.D + d, gxo);
+                if (IN ? s >= t0 : (d_ok && s >= t0 && s < t1)) stv<VEC>(gxrow + s * p.D, gxo);
             }
         }
+    }
+    };
+    if (interior) {
+        if (d_ok) body(std::true_type{});
+    } else {
+        body(std::false_type{});
     }
     if (!d_ok) return;
     const long long part = b * p.nseg + seg;
