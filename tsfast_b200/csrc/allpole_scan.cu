@@ -483,9 +483,9 @@ struct GBlockArgs {
 #define GBLOCK_BW_MINB 4  // same, numerator adjoint
 #endif
 
-template <int NA, int NB, int VEC, int W, int S>
+template <int NA, int NB, int VEC, int W, int S, int SEG>
 __global__ void __launch_bounds__(32 * W, GBLOCK_MINB) gblock_fwd_kernel(const GBlockArgs p) {
-    constexpr int kSeg = 32, kTile = 32 * kSeg, kChunk = kSeg + 4;
+    constexpr int kSeg = SEG, kTile = 32 * kSeg, kChunk = kSeg + 4;
     constexpr int kStageF = 33 * kChunk;  // 32 thread chunks + one for the NB-1 samples past the tile
     constexpr int PIECES = kTile / VEC, PPC = kSeg / VEC;
     constexpr int HALO = (NB - 1 + VEC - 1) / VEC;  // copy pieces past the tile
@@ -965,6 +965,9 @@ static int dispatch_gblock_num_bwd(int nb, const GBlockBwdArgs& a, cudaStream_t 
     }
 }
 
+#ifndef GBLOCK_SEG
+#define GBLOCK_SEG 32  // steps per thread of the forward (16 or 32)
+#endif
 #ifndef GBLOCK_W
 #define GBLOCK_W 2  // (batch row, output channel) warps per CTA
 #endif
@@ -974,13 +977,13 @@ static int dispatch_gblock_num_bwd(int nb, const GBlockBwdArgs& a, cudaStream_t 
 
 template <int NA, int NB, int VEC>
 static int launch_gblock(const GBlockArgs& a, cudaStream_t st) {
-    constexpr int W = GBLOCK_W, S = GBLOCK_S;
+    constexpr int W = GBLOCK_W, S = GBLOCK_S, SEG = (NB - 1 <= GBLOCK_SEG) ? GBLOCK_SEG : 32;
     const int I = (int)a.I;
     const size_t dper = (size_t)(((2 * NA * NA + I * (5 * NA * NA + NA)) + 1) & ~1);
-    const size_t fper = (size_t)S * 33 * 36 + 32 * 36 + (size_t)((I * NA + 3) & ~3);
+    const size_t fper = (size_t)S * 33 * (SEG + 4) + 32 * (SEG + 4) + (size_t)((I * NA + 3) & ~3);
     const size_t smem = W * (dper * sizeof(double) + fper * sizeof(float));
     if (smem > 200 * 1024) return B200_ERR_UNSUPPORTED;
-    auto kern = gblock_fwd_kernel<NA, NB, VEC, W, S>;
+    auto kern = gblock_fwd_kernel<NA, NB, VEC, W, S, SEG>;
     static size_t configured[64] = {0};  // largest size asked for so far, per device
     int dev = 0;
     cudaGetDevice(&dev);
