@@ -891,21 +891,51 @@ static int launch(const DiagArgs& a, const DiagPlan& pl, cudaStream_t st) {
 #define STRM_C_BWD_MINB 1
 #endif
 
-template <typename E, int V, bool BWD>
+// The four (dtype, constant/varying coefficient) families stream 2..5 tensors of 4- or 8-byte
+// elements, so each has its own shape (bytes per thread and tensor, warps, stages, CTAs per SM).
+#ifndef STRM_S1_FWD_BYTES
+#define STRM_S1_FWD_BYTES 64  // float32, constant coefficient: measured at M=128, L=2000, N=512 (5.5 -> 5.9 TB/s)
+#define STRM_S1_FWD_W 8
+#define STRM_S1_FWD_S 4
+#define STRM_S1_FWD_MINB 1
+#endif
+#ifndef STRM_S1_BWD_BYTES
+#define STRM_S1_BWD_BYTES 128  // (5.4 -> 6.0 TB/s)
+#define STRM_S1_BWD_W 4
+#define STRM_S1_BWD_S 3
+#define STRM_S1_BWD_MINB 1
+#endif
+#ifndef STRM_CV_FWD_BYTES
+#define STRM_CV_FWD_BYTES 128  // complex64, varying coefficient: measured at M=128, L=2000, N=256 (6.2 -> 6.4 TB/s)
+#define STRM_CV_FWD_W 4
+#define STRM_CV_FWD_S 4
+#define STRM_CV_FWD_MINB 1
+#endif
+#ifndef STRM_CV_BWD_BYTES
+#define STRM_CV_BWD_BYTES 64  // (6.0 -> 6.4 TB/s; 3.8 -> 6.0 TB/s at M=64, L=4096, N=128)
+#define STRM_CV_BWD_W 4
+#define STRM_CV_BWD_S 3
+#define STRM_CV_BWD_MINB 3
+#endif
+
+#define B200_STRM_PICK(what)                                                                              \
+    (CX ? (VARY ? (BWD ? STRM_CV_BWD_##what : STRM_CV_FWD_##what) : (BWD ? STRM_C_BWD_##what : STRM_C_FWD_##what)) \
+        : (VARY ? (BWD ? STRM_BWD_##what : STRM_FWD_##what) : (BWD ? STRM_S1_BWD_##what : STRM_S1_FWD_##what)))
+
+template <typename E, int V, bool BWD, bool VARY>
 struct StreamCfg {
     static constexpr bool CX = sizeof(E) == 8;
-    static constexpr int W = CX ? (BWD ? STRM_C_BWD_W : STRM_C_FWD_W) : (BWD ? STRM_BWD_W : STRM_FWD_W);
-    static constexpr int S = CX ? (BWD ? STRM_C_BWD_S : STRM_C_FWD_S) : (BWD ? STRM_BWD_S : STRM_FWD_S);
-    static constexpr int MINB = CX ? (BWD ? STRM_C_BWD_MINB : STRM_C_FWD_MINB) : (BWD ? STRM_BWD_MINB : STRM_FWD_MINB);
-    static constexpr int BYTES =
-        CX ? (BWD ? STRM_C_BWD_BYTES : STRM_C_FWD_BYTES) : (BWD ? STRM_BWD_BYTES : STRM_FWD_BYTES);
+    static constexpr int W = B200_STRM_PICK(W);
+    static constexpr int S = B200_STRM_PICK(S);
+    static constexpr int MINB = B200_STRM_PICK(MINB);
+    static constexpr int BYTES = B200_STRM_PICK(BYTES);
     static constexpr int TSraw = BYTES / (int)(sizeof(E) * V);
     static constexpr int TS = TSraw > 16 ? 16 : (TSraw < 1 ? 1 : TSraw);
 };
 
 template <typename E, bool VARY, bool BWD, int V>
 static int launch_stream(DiagArgs a, cudaStream_t st) {
-    using C = StreamCfg<E, V, BWD>;
+    using C = StreamCfg<E, V, BWD, VARY>;
     constexpr int NT = (VARY ? 1 : 0) + 1 + (BWD ? 1 : 0);
     constexpr size_t ring = (size_t)C::S * NT * C::TS * (32 * C::W) * sizeof(E) * V;
     auto kern = diag_stream_kernel<E, VARY, BWD, V, C::TS, C::W, C::S, C::MINB>;
