@@ -183,3 +183,40 @@ def test_unsupported_shapes_raise():
         dn.linear_block(u, torch.randn(1, 1, 17, device="cuda"), torch.randn(1, 1, 2, device="cuda"), None)
     with pytest.raises(RuntimeError):
         dn.linear_block(u.cpu(), torch.randn(1, 1, 8), torch.randn(1, 1, 2), None)
+
+
+def test_full_size_residuals():
+    """At the benchmark size (B=128, T=8192, 8 x 16 filters, nb=8, na=4) the outputs satisfy the
+    defining equations: every pair's output run back through its denominator gives the numerator
+    output (grouped conv1d of the input), the block output is the sum over inputs, and the new
+    state is the last na outputs of every pair."""
+    import torch.nn.functional as F
+
+    from tsfast_b200 import dynonet_b200 as dn
+
+    torch.manual_seed(4)
+    Bsz, L, I, O, nb, na = 128, 8192, 8, 16, 8, 4
+    P = I * O
+    u = torch.randn(Bsz, L, I, device="cuda")
+    b = torch.randn(O, I, nb, device="cuda") * 0.3
+    r, th = torch.rand(O, I, 2, device="cuda") * 0.45 + 0.5, torch.rand(O, I, 2, device="cuda") * 3.14159
+    c1, d1 = -2 * r[..., 0] * torch.cos(th[..., 0]), r[..., 0] ** 2
+    c2, d2 = -2 * r[..., 1] * torch.cos(th[..., 1]), r[..., 1] ** 2
+    a = torch.stack((c1 + c2, d1 + d2 + c1 * c2, c1 * d2 + c2 * d1, d1 * d2), -1)  # two conjugate pole pairs
+    with torch.no_grad():
+        y, yp, xl, _, _ = dn._gblock_op(u, None, b, a, None, True)
+        y_inf = dn._gblock_op(u, None, b, a, None, False)[0]
+        w = F.conv1d(torch.cat((u.new_zeros(Bsz, nb - 1, I), u), 1).transpose(1, 2),
+                     b.permute(1, 0, 2).reshape(P, 1, nb).flip(-1), groups=I)
+        a_p = a.permute(1, 0, 2).reshape(1, P, na)
+        res = yp.clone()
+        for k in range(1, na + 1):  # y_t + sum_k a_k y_{t-k} = w_t with a zero start
+            res[..., k:] += a_p[..., k - 1 : k] * yp[..., :-k]
+        # rounding of the na + 1 terms is relative to the outputs, which these poles amplify
+        bound = 1e-5 * float(yp.abs().max()) * (1 + float(a.abs().sum(-1).max()))
+        err = float((res - w).abs().max())
+        assert err < bound, (err, bound, float(w.abs().max()))
+        assert torch.equal(y, y_inf)
+        ysum = yp.view(Bsz, I, O, L).sum(1)
+        assert float((y - ysum).abs().max()) < 1e-5 * float(ysum.abs().max())
+        assert torch.equal(xl, yp[..., L - na :].flip(-1))
