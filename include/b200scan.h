@@ -111,7 +111,10 @@ int b200_allpole_bwd(int64_t lanes, int64_t L, int64_t na, const void* g, const 
  * (pad taps and tail with zeros up to the next size); pairs are indexed j*O + i as in the
  * reference.  taps [O,I,nb], a [O,I,na], x0 [B,I*O,na] or NULL (newest first), y [B,O,L] (the
  * reference returns this tensor transposed to [B,L,O] as a view), y_pairs [B,I*O,L] or NULL (the
- * per-pair outputs the adjoint b200_allpole_bwd needs), x_last [B,I*O,na].  No workspace. */
+ * per-pair outputs the adjoint needs), x_last [B,I*O,na].  With y == NULL (y_pairs required) the
+ * kernel runs one warp per filter instead of one per (batch row, output channel) and writes only the
+ * per-pair outputs, for blocks with too few outputs to fill the GPU; the caller sums them over the
+ * inputs.  No workspace. */
 int b200_gblock_fwd(int64_t B, int64_t L, int64_t I, int64_t O, int64_t na, int64_t nb, int64_t pitch,
                     const void* ub, const void* taps, const void* a, const void* x0, void* y, void* y_pairs,
                     void* x_last, void* stream);

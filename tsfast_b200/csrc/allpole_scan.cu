@@ -468,6 +468,7 @@ struct GBlockArgs {
     float* yp;         // [B, I*O, L] or null: the per-pair outputs (what the adjoint needs)
     float* xlast;      // [B, I*O, na]: last na outputs of every pair, newest first
     long long B, I, O, L, pitch;
+    int split;         // one warp per pair instead of per (b, output): y is not written, yp must be
 };
 
 #ifndef GBLOCK_BW_W
@@ -495,9 +496,15 @@ __global__ void __launch_bounds__(32 * W, GBLOCK_MINB) gblock_fwd_kernel(const G
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int w = threadIdx.x >> 5, lid = threadIdx.x & 31;
     const long long widx = (long long)blockIdx.x * W + w;
-    if (widx >= p.B * p.O) return;  // warps never synchronise with each other
-    const long long b = widx / p.O, i = widx - b * p.O;
-    const int I = (int)p.I;
+    // normally a warp owns (b, i) and walks all inputs; in split mode (few outputs: not enough
+    // (b, i) to fill the GPU) a warp owns one pair (b, j0, i) and only the per-pair outputs are written
+    const long long OV = p.split ? p.I * p.O : p.O;
+    if (widx >= p.B * OV) return;  // warps never synchronise with each other
+    const long long b = widx / OV, iv = widx - b * OV;
+    const long long i = p.split ? iv % p.O : iv;
+    const int j0 = p.split ? (int)(iv / p.O) : 0;
+    const int I = (int)p.I;          // inputs of the block (row and coefficient strides)
+    const int nj = p.split ? 1 : I;  // inputs this warp walks
     const long long L = p.L, P = p.I * p.O;
 
     // per warp: doubles [2 NA^2 scratch | I x 5 NA^2 powers | I x NA carried states], then floats
@@ -513,10 +520,10 @@ __global__ void __launch_bounds__(32 * W, GBLOCK_MINB) gblock_fwd_kernel(const G
     float* ptail = ysum + 32 * kChunk;      // [I][NA]
 
     const long long C = (L + kTile - 1) / kTile;
-    const long long items = C * I;  // item q = (tile q / I, input channel q % I)
+    const long long items = C * nj;  // item q = (tile q / nj, input channel j0 + q % nj)
 
     auto issue = [&](long long q, int slot) {
-        const long long c = q / I, j = q - c * I;
+        const long long c = q / nj, j = j0 + (q - c * nj);
         const float* src = p.ub + (b * I + j) * p.pitch + c * kTile;
         const long long room = p.pitch - c * kTile;  // samples of the row from the tile start on
         float* dst = ring + slot * kStageF;
@@ -542,7 +549,8 @@ __global__ void __launch_bounds__(32 * W, GBLOCK_MINB) gblock_fwd_kernel(const G
     }
 
     // ---------------------------------------------------------------- per pair: M^(2^d), start state
-    for (int j = 0; j < I; ++j) {
+    for (int j = j0; j < j0 + nj; ++j) {
+        const int jl = j - j0;  // index into this warp's shared-memory tables
         float aj[NA];
 #pragma unroll
         for (int k = 0; k < NA; ++k) aj[k] = p.a[(i * p.I + j) * NA + k];
@@ -561,8 +569,8 @@ __global__ void __launch_bounds__(32 * W, GBLOCK_MINB) gblock_fwd_kernel(const G
 #pragma unroll
             for (int r = 0; r < NA; ++r) Md[r * NA + lid] = s[r];
             const long long pr = b * P + j * p.O + i;
-            cins[j * NA + lid] = p.x0 != nullptr ? (double)p.x0[pr * NA + lid] : 0.0;
-            ptail[j * NA + lid] = 0.f;
+            cins[jl * NA + lid] = p.x0 != nullptr ? (double)p.x0[pr * NA + lid] : 0.0;
+            ptail[jl * NA + lid] = 0.f;
         }
         __syncwarp();
         int cur = 0;
@@ -570,7 +578,7 @@ __global__ void __launch_bounds__(32 * W, GBLOCK_MINB) gblock_fwd_kernel(const G
             const double* src = Md + cur * NA * NA;
             double* dst = Md + (cur ^ 1) * NA * NA;
             for (int e = lid; e < NA * NA; e += 32) {
-                Mp[(j * 5 + d) * NA * NA + e] = clamp_finite(src[e]);
+                Mp[(jl * 5 + d) * NA * NA + e] = clamp_finite(src[e]);
                 if (d < 4) {
                     const int r = e / NA, cc = e % NA;
                     double acc = 0.0;
@@ -591,7 +599,8 @@ __global__ void __launch_bounds__(32 * W, GBLOCK_MINB) gblock_fwd_kernel(const G
         const bool edge = t0 + kTile > L;
 #pragma unroll
         for (int r = 0; r < kSeg; ++r) yacc[r] = 0.f;
-        for (int j = 0; j < I; ++j, ++q) {
+        for (int j = j0; j < j0 + nj; ++j, ++q) {
+            const int jl = j - j0;
             const int slot = (int)(q % S);
             float* stage = ring + slot * kStageF;
             cp_wait<S - 2>();
@@ -640,11 +649,11 @@ __global__ void __launch_bounds__(32 * W, GBLOCK_MINB) gblock_fwd_kernel(const G
             for (int k = 0; k < kSeg; ++k) iir_step<NA>(a, s, v[k]);
 
             // 2. carry of the previous tile enters at thread 0; Kogge-Stone over the 32 segments
-            const double* Mj = Mp + j * 5 * NA * NA;
+            const double* Mj = Mp + jl * 5 * NA * NA;
             double cin[NA], sd[NA];
 #pragma unroll
             for (int k = 0; k < NA; ++k) {
-                cin[k] = cins[j * NA + k];
+                cin[k] = cins[jl * NA + k];
                 sd[k] = (double)s[k];
             }
             if (lid == 0) {
@@ -681,7 +690,7 @@ __global__ void __launch_bounds__(32 * W, GBLOCK_MINB) gblock_fwd_kernel(const G
 #pragma unroll
             for (int k = 0; k < NA; ++k) {
                 const double e = __shfl_sync(0xffffffffu, sd[k], 31);
-                if (lid == 0) cins[j * NA + k] = e;
+                if (lid == 0) cins[jl * NA + k] = e;
             }
 
             // 3. the true run of the segment; add the pair's output to the channel sum
@@ -719,7 +728,7 @@ __global__ void __launch_bounds__(32 * W, GBLOCK_MINB) gblock_fwd_kernel(const G
                         const int x = (int)(t - t0);
                         val = stage[(x / kSeg) * kChunk + (x % kSeg)];
                     } else if (t >= 0) {
-                        val = ptail[j * NA + (int)(t0 - 1 - t)];
+                        val = ptail[jl * NA + (int)(t0 - 1 - t)];
                     } else {
                         val = p.x0 != nullptr ? p.x0[pr * NA + (int)(-t - 1)] : 0.f;
                     }
@@ -729,10 +738,11 @@ __global__ void __launch_bounds__(32 * W, GBLOCK_MINB) gblock_fwd_kernel(const G
             __syncwarp();
             if (lid < NA && c < C - 1) {  // tail of a whole tile: y_{t0+1023-k}
                 const int x = kTile - 1 - lid;
-                ptail[j * NA + lid] = stage[(x / kSeg) * kChunk + (x % kSeg)];
+                ptail[jl * NA + lid] = stage[(x / kSeg) * kChunk + (x % kSeg)];
             }
             __syncwarp();
         }
+        if (p.y == nullptr) continue;  // split mode: the caller sums the per-pair outputs
         // the channel's tile: stage and store coalesced
 #pragma unroll
         for (int r = 0; r < kSeg / 4; ++r)
@@ -992,7 +1002,7 @@ static int launch_gblock(const GBlockArgs& a, cudaStream_t st) {
             return B200_ERR_LAUNCH;
         configured[dev] = smem;
     }
-    const long long grid = (a.B * a.O + W - 1) / W;
+    const long long grid = (a.B * (a.split ? a.I * a.O : a.O) + W - 1) / W;
     if (grid > 0x7fffffffLL) return B200_ERR_UNSUPPORTED;
     kern<<<(unsigned int)grid, 32 * W, smem, st>>>(a);
     return cudaGetLastError() == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
@@ -1029,7 +1039,7 @@ int b200_gblock_fwd(int64_t B, int64_t L, int64_t I, int64_t O, int64_t na, int6
     if (B < 0 || L < 0 || I < 1 || O < 1 || na < 1 || nb < 1 || pitch < L + nb - 1) return B200_ERR_ARG;
     if (na > 4 || (nb != 4 && nb != 8 && nb != 16)) return B200_ERR_UNSUPPORTED;
     if (B == 0) return B200_OK;
-    if (!ub || !taps || !a || !x_last || (L > 0 && !y)) return B200_ERR_ARG;
+    if (!ub || !taps || !a || !x_last || (L > 0 && !y && !y_pairs)) return B200_ERR_ARG;
     const uintptr_t por = (uintptr_t)ub | (uintptr_t)taps | (uintptr_t)a | (uintptr_t)x0 | (uintptr_t)y |
                           (uintptr_t)y_pairs | (uintptr_t)x_last;
     if (por % 4 != 0) return B200_ERR_ARG;
@@ -1042,6 +1052,7 @@ int b200_gblock_fwd(int64_t B, int64_t L, int64_t I, int64_t O, int64_t na, int6
     p.yp = static_cast<float*>(y_pairs);
     p.xlast = static_cast<float*>(x_last);
     p.B = B, p.I = I, p.O = O, p.L = L, p.pitch = pitch;
+    p.split = y == nullptr ? 1 : 0;  // without y: one warp per pair, per-pair outputs only
     const uintptr_t seq_or = (uintptr_t)ub | (uintptr_t)y | (uintptr_t)y_pairs;
     const bool vec = (L % 4 == 0) && (pitch % 4 == 0) && (seq_or % 16 == 0);
     cudaStream_t st = static_cast<cudaStream_t>(stream);

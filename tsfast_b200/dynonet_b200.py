@@ -30,6 +30,7 @@ from .allpole_b200 import _allpole_bwd_op
 __all__ = ["linear_block", "LinearDynamicalOperator", "DynoNet", "supports"]
 
 _MAX_NA = 4
+_SPLIT_BELOW = 296  # (batch row, output) warps under which the forward runs one warp per filter: 2 per SM
 _NB_SIZES = (4, 8, 16)
 
 
@@ -84,14 +85,21 @@ def _gblock_op(u: torch.Tensor, tail: torch.Tensor | None, b_coeff: torch.Tensor
     a_c = a_coeff.contiguous()
     x0_c = x0.contiguous() if x0 is not None else None
     _lib.require_dense_cuda(ub=ub, taps=taps, a=a_c, x0=x0_c)
-    y = u.new_empty(B, O, L)
-    yp = u.new_empty(B, I * O, L) if keep_pairs else u.new_empty(0)
+    # one warp per (batch row, output) walks all inputs; with too few of those to fill the GPU the
+    # kernel runs one warp per filter instead, writes the per-pair outputs only, and they are summed here
+    per_pair = I > 1 and B * O < _SPLIT_BELOW
+    y = None if per_pair else u.new_empty(B, O, L)
+    yp = u.new_empty(B, I * O, L) if (keep_pairs or per_pair) else u.new_empty(0)
     xl = u.new_empty(B, I * O, na)
     if B:
         st = _lib.lib().b200_gblock_fwd(B, L, I, O, na, NB, pitch, _lib.ptr(ub), _lib.ptr(taps), _lib.ptr(a_c),
-                                        _lib.ptr(x0_c), _lib.ptr(y), _lib.ptr(yp) if keep_pairs else None,
+                                        _lib.ptr(x0_c), _lib.ptr(y), _lib.ptr(yp) if yp.numel() else None,
                                         _lib.ptr(xl), _lib.stream_ptr(u.device))
         _lib.check(st, "b200_gblock_fwd")
+    if per_pair:
+        y = yp.view(B, I, O, L).sum(1)
+        if not keep_pairs:
+            yp = u.new_empty(0)
     return y, yp, xl, ub, taps
 
 
