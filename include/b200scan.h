@@ -119,6 +119,13 @@ int b200_gblock_fwd(int64_t B, int64_t L, int64_t I, int64_t O, int64_t na, int6
                     const void* ub, const void* taps, const void* a, const void* x0, void* y, void* y_pairs,
                     void* x_last, void* stream);
 
+/* Builds the input rows the two G-block entry points read, ub [B*I, pitch], from u [B,L,I] (channel
+ * last, dense) and the carried tail [B,nb-1,I] or NULL: row (b,j) = nb_padded-nb zeros, the tail,
+ * u[b,:,j], zeros up to the pitch.  Replaces the torch.cat + transpose that feed conv1d in
+ * dynonet/core.py:212-220. */
+int b200_gblock_pack_rows(int64_t B, int64_t L, int64_t I, int64_t nb_padded, int64_t nb, int64_t pitch,
+                          const void* u, const void* tail, void* ub, void* stream);
+
 /* Adjoint of b200_gblock_fwd for an upstream gradient gy [B,O,L] on y (same layouts, nb padded the
  * same way): the all-pole adjoint of every pair (reading gy and the [O,I,na] coefficients in
  * place through a row map, so the [B,I*O,L] broadcast of gy is never built) followed by the

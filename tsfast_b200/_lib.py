@@ -39,6 +39,7 @@ SIGNATURES = {
     "b200_sel_bwd": (_int, [_int, _i64, _i64, _i64] + [_vp] * 8 + [_sz, _vp]),
     "b200_allpole_fwd": (_int, [_i64, _i64, _i64] + [_vp] * 5),
     "b200_allpole_bwd": (_int, [_i64, _i64, _i64] + [_vp] * 8),
+    "b200_gblock_pack_rows": (_int, [_i64] * 6 + [_vp] * 4),
     "b200_gblock_fwd": (_int, [_i64] * 7 + [_vp] * 8),
     "b200_gblock_bwd_workspace_bytes": (_sz, [_i64] * 4),
     "b200_gblock_bwd": (_int, [_i64] * 7 + [_vp] * 11 + [_sz, _vp]),

@@ -975,6 +975,27 @@ static int dispatch_gblock_num_bwd(int nb, const GBlockBwdArgs& a, cudaStream_t 
     }
 }
 
+// The G-block kernels read time-contiguous input rows: ub[b, j, :] = NB-nb zeros, the carried tail
+// (nb-1 samples), u[b, :, j], zeros up to the pitch.  One thread per (batch row, position): it reads
+// the I channels of its time step (contiguous) and writes one sample into each of the I rows, so
+// that neighbouring threads read neighbouring input rows and write neighbouring samples.
+__global__ void gblock_pack_rows_kernel(const float* __restrict__ u, const float* __restrict__ tail,
+                                        float* __restrict__ ub, long long B, long long L, long long I, long long pitch,
+                                        int NBp, int nb) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= B * pitch) return;
+    const long long s_ = idx % pitch, b = idx / pitch;
+    const float* src = nullptr;
+    if (s_ >= NBp - 1) {
+        const long long t = s_ - (NBp - 1);
+        if (t < L) src = u + (b * L + t) * I;
+    } else if (s_ >= NBp - nb && tail != nullptr) {
+        src = tail + (b * (nb - 1) + (s_ - (NBp - nb))) * I;
+    }
+    float* dst = ub + b * I * pitch + s_;
+    for (long long j = 0; j < I; ++j) dst[j * pitch] = src != nullptr ? src[j] : 0.f;
+}
+
 #ifndef GBLOCK_SEG
 #define GBLOCK_SEG 32  // steps per thread of the forward (16 or 32)
 #endif
@@ -1118,6 +1139,20 @@ int b200_gblock_bwd(int64_t B, int64_t L, int64_t I, int64_t O, int64_t na, int6
     // positions of a row past NB-1 + L are not written by the kernel
     if (cudaMemsetAsync(gub, 0, (size_t)B * I * pitch * sizeof(float), st) != cudaSuccess) return B200_ERR_LAUNCH;
     return vec ? dispatch_gblock_num_bwd<4>((int)nb, p, st) : dispatch_gblock_num_bwd<1>((int)nb, p, st);
+}
+
+int b200_gblock_pack_rows(int64_t B, int64_t L, int64_t I, int64_t nb_padded, int64_t nb, int64_t pitch,
+                          const void* u, const void* tail, void* ub, void* stream) {
+    if (B < 0 || L < 0 || I < 1 || nb < 1 || nb_padded < nb || pitch < L + nb_padded - 1) return B200_ERR_ARG;
+    const long long total = B * pitch;  // one thread per (batch row, position)
+    if (total == 0) return B200_OK;
+    if (!ub || (L > 0 && !u)) return B200_ERR_ARG;
+    const long long blocks = (total + 255) / 256;
+    if (blocks > 0x7fffffffLL) return B200_ERR_UNSUPPORTED;
+    b200::gblock_pack_rows_kernel<<<(unsigned int)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const float*>(u), static_cast<const float*>(tail), static_cast<float*>(ub), B, L, I, pitch,
+        (int)nb_padded, (int)nb);
+    return cudaGetLastError() == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
 }
 
 }  // extern "C"

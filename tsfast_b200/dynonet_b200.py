@@ -54,17 +54,24 @@ def _padded_nb(nb: int) -> int:
 
 
 def _rows_and_taps(u, tail, b_coeff, NB):
-    """The kernels' input rows ``[B, I, pitch]`` (zeros, the carried tail, then ``u[b, :, j]``) and
-    the taps zero-padded to ``NB``."""
+    """The kernels' input rows ``[B, I, pitch]`` (zeros, the carried tail, then ``u[b, :, j]``; one
+    kernel, ``b200_gblock_pack_rows``) and the taps zero-padded to ``NB``."""
     B, L, I = u.shape
     O, _, nb = b_coeff.shape
     pitch = (L + NB - 1 + 3) // 4 * 4
-    ub = u.new_zeros(B, I, pitch)
-    if tail is not None and nb > 1:
-        ub[:, :, NB - nb : NB - 1] = tail.transpose(1, 2)
-    ub[:, :, NB - 1 : NB - 1 + L] = u.transpose(1, 2)
-    taps = b_coeff.new_zeros(O, I, NB)
-    taps[:, :, :nb] = b_coeff
+    u_c = u.contiguous()
+    tail_c = tail.contiguous() if (tail is not None and nb > 1) else None
+    _lib.require_dense_cuda(u=u_c, tail=tail_c)
+    ub = u.new_empty(B, I, pitch)
+    if ub.numel():
+        st = _lib.lib().b200_gblock_pack_rows(B, L, I, NB, nb, pitch, _lib.ptr(u_c), _lib.ptr(tail_c), _lib.ptr(ub),
+                                              _lib.stream_ptr(u.device))
+        _lib.check(st, "b200_gblock_pack_rows")
+    if nb == NB:
+        taps = b_coeff.clone(memory_format=torch.contiguous_format)  # an op output may not alias an input
+    else:
+        taps = b_coeff.new_zeros(O, I, NB)
+        taps[:, :, :nb] = b_coeff
     return ub, taps, pitch
 
 
