@@ -133,12 +133,14 @@ int b200_gblock_pack_rows(int64_t B, int64_t L, int64_t I, int64_t nb_padded, in
  * sum/view, tsfast::dynonet_allpole_bwd (allpole_triton.py:174-213) and the grouped conv1d
  * gradients.  Writes gub [B*I,pitch] (gradient w.r.t. the rows of ub: carried tail, then input),
  * gtaps [B,O,I,nb] and ga [B,I*O,na] (per batch row; the caller sums over B), gx0 [B,I*O,na] when
- * x0 != NULL.  The workspace holds the numerator-output gradient [B,I*O,L]. */
+ * x0 != NULL.  With gub_per_filter != 0 the numerator adjoint runs one warp per filter (for blocks
+ * with too few inputs to fill the GPU) and gub is [B*I*O,pitch], one row per pair j*O+i, which the
+ * caller sums over i.  The workspace holds the numerator-output gradient [B,I*O,L]. */
 size_t b200_gblock_bwd_workspace_bytes(int64_t B, int64_t L, int64_t I, int64_t O);
 int b200_gblock_bwd(int64_t B, int64_t L, int64_t I, int64_t O, int64_t na, int64_t nb, int64_t pitch,
                     const void* gy, const void* ub, const void* taps, const void* a, const void* y_pairs,
-                    const void* x0, void* gub, void* gtaps, void* ga, void* gx0, void* workspace,
-                    size_t workspace_bytes, void* stream);
+                    const void* x0, void* gub, int64_t gub_per_filter, void* gtaps, void* ga, void* gx0,
+                    void* workspace, size_t workspace_bytes, void* stream);
 
 /* ---- S3: fused Mamba selective-scan section ---------------------------------------------
  * delta = softplus(draw) (threshold 20); h_t = exp(delta_t A) h_{t-1} + delta_t u_t B_t;

@@ -43,7 +43,17 @@ def _run(u, b, a, tail, x0, g=None):
     return out
 
 
-def test_golden():
+@pytest.fixture(params=["per_row", "per_filter"])
+def warp_split(request, monkeypatch):
+    """Both work splits must pass: a warp per (batch row, channel) walking the other channel axis,
+    and (chosen for blocks too small to fill the GPU) a warp per filter with the sum done outside."""
+    from tsfast_b200 import dynonet_b200 as dn
+
+    monkeypatch.setattr(dn, "_SPLIT_BELOW", 0 if request.param == "per_row" else 10**9)
+    return request.param
+
+
+def test_golden(warp_split):
     for c in load_golden("gblock"):
         r = _run(c.u, c.b, c.a, c.tail, c.x0, c.g)
         keys = ["y", "tail", "xlast", "gu", "gb", "ga"] + (["gtail", "gx0"] if c.tail is not None else [])
@@ -51,7 +61,7 @@ def test_golden():
             assert rel_err(r[k], getattr(c, "ref64_" + k)) < REL, (c.name, k)
 
 
-def test_golden_without_autograd_matches():
+def test_golden_without_autograd_matches(warp_split):
     """The inference path (no per-pair outputs kept) gives the same numbers."""
     for c in load_golden("gblock"):
         with torch.no_grad():
@@ -69,7 +79,7 @@ SHAPES = [(2, 1, 1, 1, 8, 2, True), (1, 2, 2, 2, 4, 4, True), (3, 1023, 2, 3, 8,
 
 
 @pytest.mark.parametrize("shape", SHAPES, ids=lambda s: "x".join(map(str, s[:6])) + ("s" if s[6] else ""))
-def test_matches_oracle(oracle, shape):
+def test_matches_oracle(oracle, warp_split, shape):
     Bsz, L, I, O, nb, na, with_state = shape
     rng = np.random.default_rng(sum(p * q for p, q in zip(shape[:6], (7, 11, 13, 17, 19, 23))))
     u = rng.standard_normal((Bsz, L, I)).astype(np.float32)
@@ -89,7 +99,7 @@ def test_matches_oracle(oracle, shape):
         assert rel_err(r["gx0"], gx0) < REL, (shape, "gx0")
 
 
-def test_chunked_rollout_equals_full_sequence():
+def test_chunked_rollout_equals_full_sequence(warp_split):
     """Feeding the returned state back continues the sequence (reference tests/test_dynonet.py stateful checks)."""
     from tsfast_b200 import dynonet_b200 as dn
 
@@ -108,7 +118,7 @@ def test_chunked_rollout_equals_full_sequence():
     assert rel_err(torch.cat(parts, 1).cpu().numpy(), full.cpu().numpy()) < 1e-5
 
 
-def test_gradient_through_the_new_state():
+def test_gradient_through_the_new_state(warp_split):
     """A loss on the returned filter state as well: the general adjoint against the reference's
     formulation (grouped conv1d, all-pole op, slices) differentiated by autograd."""
     import torch.nn.functional as F

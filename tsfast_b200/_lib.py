@@ -42,7 +42,7 @@ SIGNATURES = {
     "b200_gblock_pack_rows": (_int, [_i64] * 6 + [_vp] * 4),
     "b200_gblock_fwd": (_int, [_i64] * 7 + [_vp] * 8),
     "b200_gblock_bwd_workspace_bytes": (_sz, [_i64] * 4),
-    "b200_gblock_bwd": (_int, [_i64] * 7 + [_vp] * 11 + [_sz, _vp]),
+    "b200_gblock_bwd": (_int, [_i64] * 7 + [_vp] * 7 + [_i64] + [_vp] * 4 + [_sz, _vp]),
     "b200_mamba_chk_interval": (_int, []),
     "b200_mamba_fwd": (_int, [_i64] * 4 + [_vp] * 12),
     "b200_mamba_bwd_workspace_bytes": (_sz, [_i64] * 4),

@@ -776,9 +776,10 @@ struct GBlockBwdArgs {
     const float* gw;    // [B, I*O, L]
     const float* ub;    // [B*I, pitch]
     const float* taps;  // [O, I, NB]
-    float* gub;         // [B*I, pitch]
+    float* gub;         // [B*I, pitch]; split mode: [B*I*O, pitch], one row per pair
     float* gtaps;       // [B, O, I, NB]
     long long B, I, O, L, pitch;
+    int split;          // one warp per pair instead of per (b, input)
 };
 
 template <int NB, int VEC, int W, int S>
@@ -788,10 +789,19 @@ __global__ void __launch_bounds__(32 * W, GBLOCK_BW_MINB) gblock_num_bwd_kernel(
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int w = threadIdx.x >> 5, lid = threadIdx.x & 31;
     const long long widx = (long long)blockIdx.x * W + w;
-    if (widx >= p.B * p.I) return;  // warps never synchronise with each other
-    const long long b = widx / p.I, j = widx - b * p.I;
-    const int O = (int)p.O;
-    const long long L = p.L, P = p.I * p.O;
+    // normally a warp owns (b, j) and walks all outputs; in split mode (few inputs: not enough (b, j)
+    // to fill the GPU) a warp owns one pair and writes that pair's input-gradient row, which the
+    // caller sums over the outputs
+    const long long P = p.I * p.O;
+    const long long IV = p.split ? P : p.I;
+    if (widx >= p.B * IV) return;  // warps never synchronise with each other
+    const long long b = widx / IV, jv = widx - b * IV;
+    const long long j = p.split ? jv / p.O : jv;
+    const int i0 = p.split ? (int)(jv % p.O) : 0;
+    const int O = (int)p.O;              // outputs of the block (sizes the shared-memory tables)
+    const int ni = p.split ? 1 : O;      // outputs this warp walks
+    const long long L = p.L;
+    const long long orow = p.split ? b * P + j * p.O + i0 : b * p.I + j;  // row of gub this warp writes
 
     const int fper = (S + 3) * kStageF + 32 * kChunk + O * NB * 32;
     float* ring = reinterpret_cast<float*>(smem_raw) + (size_t)w * fper;  // [S] gw tiles
@@ -803,7 +813,7 @@ __global__ void __launch_bounds__(32 * W, GBLOCK_BW_MINB) gblock_num_bwd_kernel(
     __syncwarp();
 
     const long long C = (L + kTile - 1) / kTile;
-    const long long items = C * O;  // item q = (tile q / O, output channel q % O)
+    const long long items = C * ni;  // item q = (tile q / ni, output channel i0 + q % ni)
     auto copy_tile = [&](float* dst, const float* src, long long room) {
 #pragma unroll
         for (int r = 0; r < PIECES / 32; ++r) {
@@ -821,10 +831,10 @@ __global__ void __launch_bounds__(32 * W, GBLOCK_BW_MINB) gblock_num_bwd_kernel(
         }
     };
     auto issue = [&](long long q, int slot) {
-        const long long c = q / O, i = q - c * O;
+        const long long c = q / ni, i = i0 + (q - c * ni);
         // gw rows are L long (L % 4 == 0 when VEC == 4): whole pieces only below L
         copy_tile(ring + slot * kStageF, p.gw + (b * P + j * p.O + i) * L + c * kTile, L - c * kTile);
-        if (i == 0) copy_tile(ubuf + (int)(c % 3) * kStageF, p.ub + (b * p.I + j) * p.pitch + c * kTile, p.pitch - c * kTile);
+        if (i == i0) copy_tile(ubuf + (int)(c % 3) * kStageF, p.ub + (b * p.I + j) * p.pitch + c * kTile, p.pitch - c * kTile);
     };
 #pragma unroll
     for (int q = 0; q < S - 1; ++q) {
@@ -835,7 +845,7 @@ __global__ void __launch_bounds__(32 * W, GBLOCK_BW_MINB) gblock_num_bwd_kernel(
     // gradient of the carried tail: gub[s] for s < NB-1 gathers gw[s - (NB-1) + k], k >= NB-1-s
     if (lid < NB - 1) {
         float acc = 0.f;
-        for (int i = 0; i < O; ++i) {
+        for (int i = i0; i < i0 + ni; ++i) {
             const float* g = p.gw + (b * P + j * p.O + i) * L;
             const float* bt = p.taps + ((long long)i * p.I + j) * NB;
             for (int k = NB - 1 - lid; k < NB; ++k) {
@@ -843,21 +853,21 @@ __global__ void __launch_bounds__(32 * W, GBLOCK_BW_MINB) gblock_num_bwd_kernel(
                 if (t < L) acc = fmaf(bt[k], g[t], acc);
             }
         }
-        p.gub[(b * p.I + j) * p.pitch + lid] = acc;
+        p.gub[orow * p.pitch + lid] = acc;
     }
 
-    float* grow = p.gub + (b * p.I + j) * p.pitch + (NB - 1);
+    float* grow = p.gub + orow * p.pitch + (NB - 1);
     long long q = 0;
     for (long long c = 0; c < C; ++c) {
         const long long t0 = c * kTile, tbase = t0 + lid * kSeg;
         float uc[NU], guacc[kSeg];
 #pragma unroll
         for (int r = 0; r < kSeg; ++r) guacc[r] = 0.f;
-        for (int i = 0; i < O; ++i, ++q) {
+        for (int i = i0; i < i0 + ni; ++i, ++q) {
             float* stage = ring + (int)(q % S) * kStageF;
             cp_wait<S - 2>();
             __syncwarp();
-            if (i == 0) {  // this tile's input samples: own chunk and the first NB-1 of the next one
+            if (i == i0) {  // this tile's input samples: own chunk and the first NB-1 of the next one
                 const float* ut = ubuf + (int)(c % 3) * kStageF;
 #pragma unroll
                 for (int r = 0; r < kSeg / 4; ++r) {
@@ -911,7 +921,7 @@ __global__ void __launch_bounds__(32 * W, GBLOCK_BW_MINB) gblock_num_bwd_kernel(
                 for (int k = 0; k < NB; ++k) acc = fmaf(bt[k], gc[r + k], acc);
                 guacc[r] = acc;
             }
-            float* gb = gbs + (i * NB) * 32 + lid;
+            float* gb = gbs + ((i - i0) * NB) * 32 + lid;
 #pragma unroll
             for (int k = 0; k < NB; ++k) {
                 float acc = 0.f;
@@ -936,10 +946,10 @@ __global__ void __launch_bounds__(32 * W, GBLOCK_BW_MINB) gblock_num_bwd_kernel(
     }
     cp_wait<0>();
     __syncwarp();
-    for (int e = lid; e < O * NB; e += 32) {  // e = i*NB + k: add the 32 lane sums in lane order
+    for (int e = lid; e < ni * NB; e += 32) {  // e = (i-i0)*NB + k: add the 32 lane sums in lane order
         float acc = 0.f;
         for (int l = 0; l < 32; ++l) acc += gbs[e * 32 + l];
-        const int i = e / NB, k = e - i * NB;
+        const int i = i0 + e / NB, k = e % NB;
         p.gtaps[((b * p.O + i) * p.I + j) * NB + k] = acc;
     }
 }
@@ -959,7 +969,7 @@ static int launch_gblock_num_bwd(const GBlockBwdArgs& a, cudaStream_t st) {
             return B200_ERR_LAUNCH;
         configured[dev] = smem;
     }
-    const long long grid = (a.B * a.I + W - 1) / W;
+    const long long grid = (a.B * (a.split ? a.I * a.O : a.I) + W - 1) / W;
     if (grid > 0x7fffffffLL) return B200_ERR_UNSUPPORTED;
     kern<<<(unsigned int)grid, 32 * W, smem, st>>>(a);
     return cudaGetLastError() == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
@@ -1104,16 +1114,17 @@ size_t b200_gblock_bwd_workspace_bytes(int64_t B, int64_t L, int64_t I, int64_t 
 
 int b200_gblock_bwd(int64_t B, int64_t L, int64_t I, int64_t O, int64_t na, int64_t nb, int64_t pitch,
                     const void* gy, const void* ub, const void* taps, const void* a, const void* y_pairs,
-                    const void* x0, void* gub, void* gtaps, void* ga, void* gx0, void* workspace,
-                    size_t workspace_bytes, void* stream) {
+                    const void* x0, void* gub, int64_t gub_per_filter, void* gtaps, void* ga, void* gx0,
+                    void* workspace, size_t workspace_bytes, void* stream) {
     using namespace b200;
+    const int64_t gub_rows = gub_per_filter ? B * I * O : B * I;
     if (B < 0 || L < 0 || I < 1 || O < 1 || na < 1 || nb < 1 || pitch < L + nb - 1) return B200_ERR_ARG;
     if (na > 4 || (nb != 4 && nb != 8 && nb != 16)) return B200_ERR_UNSUPPORTED;
     if (B == 0) return B200_OK;
     if (!ub || !taps || !a || !gub || !gtaps || !ga || (x0 && !gx0)) return B200_ERR_ARG;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (L == 0) {  // nothing flows through an empty chunk: zero gradients, the state passes through
-        cudaError_t e = cudaMemsetAsync(gub, 0, (size_t)B * I * pitch * sizeof(float), st);
+        cudaError_t e = cudaMemsetAsync(gub, 0, (size_t)gub_rows * pitch * sizeof(float), st);
         if (e == cudaSuccess) e = cudaMemsetAsync(gtaps, 0, (size_t)B * O * I * nb * sizeof(float), st);
         if (e == cudaSuccess) e = cudaMemsetAsync(ga, 0, (size_t)B * I * O * na * sizeof(float), st);
         if (e == cudaSuccess && gx0) e = cudaMemsetAsync(gx0, 0, (size_t)B * I * O * na * sizeof(float), st);
@@ -1133,11 +1144,12 @@ int b200_gblock_bwd(int64_t B, int64_t L, int64_t I, int64_t O, int64_t na, int6
     p.gub = static_cast<float*>(gub);
     p.gtaps = static_cast<float*>(gtaps);
     p.B = B, p.I = I, p.O = O, p.L = L, p.pitch = pitch;
+    p.split = gub_per_filter ? 1 : 0;
     const uintptr_t por = (uintptr_t)ub | (uintptr_t)taps | (uintptr_t)gub | (uintptr_t)gtaps;
     if (por % 4 != 0) return B200_ERR_ARG;
     const bool vec = (L % 4 == 0) && (pitch % 4 == 0) && (((uintptr_t)ub | (uintptr_t)workspace) % 16 == 0);
     // positions of a row past NB-1 + L are not written by the kernel
-    if (cudaMemsetAsync(gub, 0, (size_t)B * I * pitch * sizeof(float), st) != cudaSuccess) return B200_ERR_LAUNCH;
+    if (cudaMemsetAsync(gub, 0, (size_t)gub_rows * pitch * sizeof(float), st) != cudaSuccess) return B200_ERR_LAUNCH;
     return vec ? dispatch_gblock_num_bwd<4>((int)nb, p, st) : dispatch_gblock_num_bwd<1>((int)nb, p, st);
 }
 

@@ -133,7 +133,10 @@ def _gblock_bwd_op(gy: torch.Tensor, ub: torch.Tensor, taps: torch.Tensor, a_coe
     gy_c, a_c, yp_c = gy.contiguous(), a_coeff.contiguous(), yp.contiguous()
     x0_c = x0.contiguous() if x0 is not None else None
     _lib.require_dense_cuda(gy=gy_c, ub=ub, taps=taps, a=a_c, x0=x0_c, y_pairs=yp_c)
-    gub = u.new_empty(B, I, pitch)
+    # one warp per (batch row, input) walks all outputs; with too few of those the numerator adjoint
+    # runs one warp per filter, writes one input-gradient row per pair, and they are summed here
+    per_pair = O > 1 and B * I < _SPLIT_BELOW
+    gub = u.new_empty(B, I * O if per_pair else I, pitch)
     gtaps = u.new_empty(B, O, I, NB)
     ga_l = u.new_empty(B, I * O, na)
     gx0 = u.new_empty(B, I * O, na) if x0 is not None else None
@@ -141,9 +144,12 @@ def _gblock_bwd_op(gy: torch.Tensor, ub: torch.Tensor, taps: torch.Tensor, a_coe
         nbytes = _lib.lib().b200_gblock_bwd_workspace_bytes(B, L, I, O)
         ws = _lib.workspace(nbytes, u.device)
         st = _lib.lib().b200_gblock_bwd(B, L, I, O, na, NB, pitch, _lib.ptr(gy_c), _lib.ptr(ub), _lib.ptr(taps),
-                                        _lib.ptr(a_c), _lib.ptr(yp_c), _lib.ptr(x0_c), _lib.ptr(gub), _lib.ptr(gtaps),
-                                        _lib.ptr(ga_l), _lib.ptr(gx0), _lib.ptr(ws), ws.numel(), _lib.stream_ptr(u.device))
+                                        _lib.ptr(a_c), _lib.ptr(yp_c), _lib.ptr(x0_c), _lib.ptr(gub), int(per_pair),
+                                        _lib.ptr(gtaps), _lib.ptr(ga_l), _lib.ptr(gx0), _lib.ptr(ws), ws.numel(),
+                                        _lib.stream_ptr(u.device))
         _lib.check(st, "b200_gblock_bwd")
+    if per_pair:
+        gub = gub.view(B, I, O, pitch).sum(2)
     gu = gub[:, :, NB - 1 : NB - 1 + L].transpose(1, 2).clone(memory_format=torch.contiguous_format)
     gtail = gub[:, :, NB - nb : NB - 1].transpose(1, 2).clone(memory_format=torch.contiguous_format)
     gb = gtaps.sum(0)[:, :, :nb].clone(memory_format=torch.contiguous_format)
