@@ -6,7 +6,7 @@ h0 = 0, upstream gradient ~ N(0,1), all synthetic and seeded.  One step = one fo
 of compulsory HBM traffic, the figure every GB/s number below is computed from.  With N GPUs every
 rank scans its own 64 sequences (weak scaling; the scan has no collective).
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload C1..C5]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload C1..C5|G|V]
 
 Prints ONE JSON line: `value` is device-resident throughput (inputs already in HBM), `e2e` the
 same metric through the public API from pinned HOST buffers with the host<->device copies inside
@@ -14,7 +14,8 @@ the timed region, `roofline` the dominant kernel (the adjoint) against the measu
 `cpu_baseline` the CPU oracle (a C port of the reference's CPU kernels) on the host cores.
 `--impl reference` times that CPU port alone and prints the same line shape.
 `--workload C1|C3|C4|C5|G|V` measures the other configurations the same way (complex LRU scan, Mamba
-section, all-pole filter, DeepLRU data-parallel training step); C2 is the headline.
+section, all-pole filter, DeepLRU data-parallel training step; G the fused dynoNet block, V the
+Mamba causal conv + SiLU); C2 is the headline.
 """
 
 from __future__ import annotations
