@@ -422,6 +422,7 @@ def _workload(name, torch, dev, rank):
                     fwd_bytes=4 * big + 2 * small + Bn * D * N * 4, bwd_bytes=7 * big + 4 * small,
                     elems=2 * Bn * L * D * N, rows=Bn, sample_rows=2, flush=False, h2d=4 * big + 2 * small + big,
                     d2h=4 * big + 2 * small, dtype="f32", launches=6, kernel="mamba_bwd_kernel<TPC=4> (b200_mamba_bwd)",
+                    traffic=815_733_248 + 499_814_144,  # ncu dram read + write of the adjoint launch, profiles/mamba_scan_c3_ncu_full.md
                     fwd=lambda: mamba_b200._scan_train_op(*ins), bwd=lambda o: mamba_b200._scan_bwd_op(gout, None, o[2], *ins),
                     e2e=e2e, cpu=cpu)
     if name == "C4":
@@ -457,6 +458,7 @@ def _workload(name, torch, dev, rank):
         return dict(desc="C4: dynoNet all-pole IIR scan fwd+bwd, B=128 x 128 channels, T=8192 fp32, order 4",
                     fwd_bytes=2 * E, bwd_bytes=3 * E, elems=2 * Bn * P * L, rows=Bn, sample_rows=8, flush=False,
                     h2d=2 * E, d2h=2 * E, dtype="f32", launches=2, kernel="allpole_kernel<NA=4, adjoint> (b200_allpole_bwd)",
+                    traffic=1_074_100_000 + 501_500_000,  # ncu dram read + write of the adjoint launch, profiles/allpole_scan_c4_ncu_full.md
                     fwd=lambda: allpole_b200._allpole_op(a, w, None), bwd=lambda o: allpole_b200._allpole_bwd_op(g, a, o, None),
                     e2e=e2e, cpu=cpu)
     if name == "V":
@@ -486,6 +488,7 @@ def _workload(name, torch, dev, rank):
         return dict(desc="V: Mamba causal depthwise conv (K=4) + SiLU fwd+bwd, B=32 T=2048 D=512 fp32 (the step feeding C3)",
                     fwd_bytes=2 * E, bwd_bytes=3 * E, elems=2 * Bn * L * D, rows=Bn, sample_rows=8, flush=False,
                     h2d=2 * E, d2h=2 * E, dtype="f32", launches=4, kernel="conv_silu_bwd_kernel<K=4> + partial sums (b200_conv_silu_bwd)",
+                    traffic=286_489_088 + 96_544_000,  # ncu dram read + write of the adjoint kernel, profiles/conv_silu_ncu_full.md
                     fwd=lambda: conv_b200._conv_silu_op(x, tail, w, bias),
                     bwd=lambda o: conv_b200._conv_silu_bwd_op(gy, x, tail, w, bias), e2e=e2e, cpu=cpu)
     if name == "G":
@@ -651,7 +654,7 @@ def run_workload(args):
                        "timing": "CUDA events around every step (enqueued behind an L2-flushing write so that host launch time is not inside), averaged", "sharding": "independent sequences per rank, no collective",
                        **extra},
             "roofline": {"bound": "hbm", "kernel": wl["kernel"], "achieved": round(bwd_gbs, 1), "peak": peak, "unit": "GB/s",
-                         "frac": round(bwd_gbs / peak, 4), "traffic": None, "peak_source": peak_src,
+                         "frac": round(bwd_gbs / peak, 4), "traffic": wl.get("traffic"), "peak_source": peak_src,
                          "algorithmic_bytes_per_launch": wl["bwd_bytes"], "ms_per_launch": round(bwd_ms, 4),
                          "forward_kernel": {"achieved": round(fwd_gbs, 1), "frac": round(fwd_gbs / peak, 4),
                                             "algorithmic_bytes_per_launch": wl["fwd_bytes"], "ms_per_launch": round(fwd_ms, 4)}},
