@@ -3,13 +3,18 @@
  * Plain pointers and sizes only.  Every tensor argument is a DEVICE pointer to a dense,
  * contiguous buffer in the layout stated per function; complex64 is interleaved (re, im)
  * float pairs.  `stream` is a cudaStream_t passed as void*.  All work is enqueued on that
- * stream; no entry point synchronises, allocates or frees device memory (so calls are legal
- * during CUDA-graph capture), and none keeps mutable global state, so concurrent calls from
- * several host threads are fine as long as each uses its own workspace.
+ * stream; no entry point except the two *_status readers synchronises, and none allocates or
+ * frees device memory (so calls are legal during CUDA-graph capture).  The library keeps no
+ * mutable state between calls apart from per-device caches filled on first use (SM count,
+ * kernel attributes, the address of the static scratch array): make the first call of each
+ * entry point on a device from one thread; after that, concurrent calls from several host
+ * threads are fine as long as each uses its own workspace.  b200_diag_fwd_static is the one
+ * exception: all its calls share one array (see there).
  *
  * Return value: B200_OK, or a B200_ERR_* code for an argument the host side can reject.  A
- * kernel that gives up on a bounded wait records B200_ERR_TIMEOUT in its workspace header;
- * b200_workspace_status() reads that word back (it synchronises the stream).
+ * kernel that gives up on a bounded wait records B200_ERR_TIMEOUT in its workspace header and
+ * finishes with a zero carry; b200_workspace_status() reads that word back (it synchronises
+ * the stream), so a caller that wants the check makes it between steps.
  *
  * Paths in the "replaces" notes are relative to the tsfast project root (v0.5.0).
  */
@@ -73,6 +78,25 @@ int b200_diag_bwd(int dtype, int64_t M, int64_t L, int64_t N, const void* g, con
  *  - it calls no cudaMalloc/cudaFree and no allocating library routine. */
 int b200_diag_fwd_static(int dtype, int64_t M, int64_t L, int64_t N, const void* lam, const void* v,
                          const void* x0, void* out, void* stream);
+/* Device-side status of the b200_diag_fwd_static calls enqueued on `stream` so far (the error
+ * word at the head of the shared array): B200_OK or B200_ERR_TIMEOUT.  Synchronises `stream`,
+ * allocates nothing.  (No counterpart in the reference.) */
+int b200_diag_static_status(void* stream);
+
+/* Test and tuning probe for S1/S2: the same launch path as b200_diag_* / b200_sel_* with the
+ * choices the regular entry points make themselves handed in.  mode 0 = kernel chosen by shape,
+ * 1 = look-back tiles, 2 = streaming chains; vcap caps the streaming kernel's vector width
+ * (0 = none); spin_limit is the number of polls a look-back wait makes before it gives up
+ * (0 = the default, about a second); mute_tile >= 0 names one look-back tile that publishes
+ * nothing, so that its successors' waits run out, the launch records B200_ERR_TIMEOUT and still
+ * returns (-1 = none).  varying selects S2, backward the adjoint; lam/val/xsrc/x0/out/glam/gx0
+ * as in the regular entry points (val = v forward, g backward; xsrc = forward output, backward
+ * only).  The workspace is the one b200_diag/sel_workspace_bytes sizes.  (No counterpart in the
+ * reference.) */
+int b200_diag_probe(int mode, int vcap, int spin_limit, int64_t mute_tile, int dtype, int varying, int backward,
+                    int64_t M, int64_t L, int64_t N, const void* lam, const void* val, const void* xsrc,
+                    const void* x0, void* out, void* glam, void* gx0, void* workspace, size_t workspace_bytes,
+                    void* stream);
 
 /* ---- S2: diagonal scan with time-varying coefficients ---------------------------------
  * x_t = lam_t * x_{t-1} + v_t.   lam, v, out [B,L,N]; x0 [B,N] or NULL.

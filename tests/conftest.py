@@ -13,6 +13,39 @@ if str(ROOT) not in sys.path:
 GOLDEN = Path(__file__).resolve().parent / "golden"
 
 
+def reference_checkout():
+    """Folder holding an importable, unmodified tsfast: ``$TSFAST_CHECKOUT`` or the copy that
+    ``oracle/make_ref.py`` places under ``oracle/_ref``; None when neither exists."""
+    import os
+
+    env = os.environ.get("TSFAST_CHECKOUT")
+    for cand in ([Path(env)] if env else []) + [ROOT / "oracle" / "_ref"]:
+        if (cand / "tsfast" / "models" / "_core" / "scan.py").exists():
+            return cand
+    return None
+
+
+def import_tsfast_models():
+    """``tsfast.models`` from the reference checkout (skips the calling test when unavailable).
+
+    tsfast compiles its CPU kernels at run time with ``$CXX``; the system g++ is named because some
+    images export a compiler without OpenMP support."""
+    import os
+
+    ref = reference_checkout()
+    if ref is None:
+        pytest.skip("no tsfast checkout (run `python oracle/make_ref.py <checkout>` or set TSFAST_CHECKOUT)")
+    os.environ.setdefault("CXX", "/usr/bin/g++")
+    os.environ.setdefault("CC", "/usr/bin/gcc")
+    if str(ref) not in sys.path:
+        sys.path.insert(0, str(ref))
+    try:
+        import tsfast.models as m
+    except Exception as e:  # a dependency of tsfast is missing on this machine
+        pytest.skip(f"tsfast not importable: {e!r}")
+    return m
+
+
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200)")
 

@@ -7,7 +7,9 @@ Public surface:
 * ``scan_backends.diagonal_b200`` / ``selective_b200`` – backend modules speaking tsfast's
   ``supports/forward/backward`` protocol;
 * ``install()`` / ``uninstall()`` – plug those modules into an importable tsfast so that its LRU,
-  S5, Mamba and dynoNet modules dispatch to these kernels.
+  S5, Mamba and dynoNet modules dispatch to these kernels;
+* ``track_status()`` / ``check_status()`` – opt-in read-back of the look-back kernels' device-side
+  error word between steps.
 
 Everything runs through ``libb200scan.so`` (``python -m tsfast_b200.build``); nothing here falls
 back to PyTorch or the CPU.
@@ -16,6 +18,7 @@ back to PyTorch or the CPU.
 from . import allpole_b200, conv_b200, dynonet_b200, mamba_b200
 from .scan import diagonal_recurrence, selective_recurrence
 from .install import install, uninstall
+from .status import check_status, track_status
 
-__all__ = ["diagonal_recurrence", "selective_recurrence", "install", "uninstall"]
+__all__ = ["diagonal_recurrence", "selective_recurrence", "install", "uninstall", "track_status", "check_status"]
 __version__ = "0.1.0"

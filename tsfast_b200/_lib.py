@@ -34,6 +34,8 @@ SIGNATURES = {
     "b200_diag_fwd": (_int, [_int, _i64, _i64, _i64] + [_vp] * 5 + [_sz, _vp]),
     "b200_diag_bwd": (_int, [_int, _i64, _i64, _i64] + [_vp] * 8 + [_sz, _vp]),
     "b200_diag_fwd_static": (_int, [_int, _i64, _i64, _i64] + [_vp] * 5),
+    "b200_diag_static_status": (_int, [_vp]),
+    "b200_diag_probe": (_int, [_int, _int, _int, _i64, _int, _int, _int, _i64, _i64, _i64] + [_vp] * 8 + [_sz, _vp]),
     "b200_sel_workspace_bytes": (_sz, [_int, _int, _i64, _i64, _i64]),
     "b200_sel_fwd": (_int, [_int, _i64, _i64, _i64] + [_vp] * 5 + [_sz, _vp]),
     "b200_sel_bwd": (_int, [_int, _i64, _i64, _i64] + [_vp] * 8 + [_sz, _vp]),
@@ -112,6 +114,6 @@ def require_dense_cuda(**tensors) -> None:
             raise TypeError(f"{name} must be contiguous")
 
 
-def last_status(ws: torch.Tensor) -> int:
+def workspace_status(ws: torch.Tensor) -> int:
     """Device-side status of the launch that used ``ws`` (synchronises the current stream)."""
     return int(lib().b200_workspace_status(ptr(ws), stream_ptr(ws.device)))

@@ -13,62 +13,45 @@ from __future__ import annotations
 
 import torch
 
-from . import _lib
+from . import _lib, _spec
 
-__all__ = ["supports", "run"]
+__all__ = ["supports", "run", "calls"]
 
-_MAX_NA = 16
+calls = 0  # launches through this module since import (the drop-in tests read it)
+
+_ORDER = {"na": (1, 16)}
+# what run() accepts: coefficients and state spread over the leading dims of w
+_PUBLIC = _spec.Contract(
+    op="dynonet_allpole",
+    tensors=(_spec.Tensor("w", (..., "L")), _spec.Tensor("a", ("na",), spread=True, over="w"),
+             _spec.Tensor("y0", ("na",), optional=True, spread=True, over="w")),
+    dtypes=(torch.float32,), ranges=_ORDER)
+# what the ops take: one row per lane
+_ON_LANES = _spec.Contract(
+    op="dynonet_allpole",
+    tensors=(_spec.Tensor("w", ("lanes", "L")), _spec.Tensor("a", ("lanes", "na")),
+             _spec.Tensor("y0", ("lanes", "na"), optional=True)),
+    dtypes=(torch.float32,), ranges=_ORDER)
 
 
 def supports(a: torch.Tensor, w: torch.Tensor, y0: torch.Tensor | None) -> str | None:
     """Reason these tensors cannot be handled, or None when they can."""
-    if not torch.cuda.is_available():
-        return "CUDA not available"
-    if w.device.type != "cuda" or a.device.type != "cuda" or (y0 is not None and y0.device.type != "cuda"):
-        return "inputs not on CUDA"
-    if any(t is not None and t.dtype != torch.float32 for t in (a, w, y0)):
-        return "needs float32 tensors"
     if w.dim() < 2:
-        return "w must have at least a batch and a time axis"
-    na = a.shape[-1]
-    if not 1 <= na <= _MAX_NA:
-        return f"na={na} outside the supported range [1, {_MAX_NA}]"
-    lead = w.shape[:-1]
-    try:
-        if torch.broadcast_shapes(a.shape[:-1], lead) != lead:
-            return f"a leading dims {tuple(a.shape[:-1])} do not broadcast into {tuple(lead)}"
-        if y0 is not None and torch.broadcast_shapes(y0.shape[:-1], lead) != lead:
-            return f"y0 leading dims {tuple(y0.shape[:-1])} do not broadcast into {tuple(lead)}"
-    except RuntimeError as e:
-        return f"shape mismatch: {e}"
-    if y0 is not None and y0.shape[-1] != na:
-        return f"y0 state dim {y0.shape[-1]} != na {na}"
-    return None
-
-
-def _check_lane_layout(a, w, y0, name):
-    if w.dim() != 2 or a.dim() != 2 or a.shape[0] != w.shape[0] or not 1 <= a.shape[1] <= _MAX_NA:
-        raise RuntimeError(f"b200scan::{name}: expected a [lanes, na<=16] and w [lanes, L], got "
-                           f"{tuple(a.shape)} and {tuple(w.shape)}")
-    if y0 is not None and y0.shape != a.shape:
-        raise RuntimeError(f"b200scan::{name}: y0 {tuple(y0.shape)} must match a {tuple(a.shape)}")
-    for t in (a, w, y0):
-        if t is not None and t.dtype != torch.float32:
-            raise RuntimeError(f"b200scan::{name}: needs float32 tensors")
-    _lib.require_dense_cuda(a=a, w=w, y0=y0)
+        return "w needs a lane axis and a time axis"
+    return _spec.explain(_PUBLIC, w=w, a=a, y0=y0)
 
 
 @torch.library.custom_op("b200scan::dynonet_allpole", mutates_args=())
 def _allpole_op(a: torch.Tensor, w: torch.Tensor, y0: torch.Tensor | None) -> torch.Tensor:
-    a, w = a.contiguous(), w.contiguous()
-    y0 = y0.contiguous() if y0 is not None else None
-    _check_lane_layout(a, w, y0, "dynonet_allpole")
-    lanes, L = w.shape
+    global calls
+    a, w, y0 = _spec.dense(a, w, y0)
+    _spec.demand(_ON_LANES, w=w, a=a, y0=y0)
     y = torch.empty_like(w)
     if y.numel():
-        st = _lib.lib().b200_allpole_fwd(lanes, L, a.shape[1], _lib.ptr(a), _lib.ptr(w), _lib.ptr(y0), _lib.ptr(y),
-                                         _lib.stream_ptr(w.device))
-        _lib.check(st, "b200_allpole_fwd")
+        calls += 1
+        lanes, steps = w.shape
+        _lib.check(_lib.lib().b200_allpole_fwd(lanes, steps, a.shape[1], _lib.ptr(a), _lib.ptr(w), _lib.ptr(y0),
+                                               _lib.ptr(y), _lib.stream_ptr(w.device)), "b200_allpole_fwd")
     return y
 
 
@@ -81,49 +64,45 @@ def _(a, w, y0):
 def _allpole_bwd_op(
     g: torch.Tensor, a: torch.Tensor, y: torch.Tensor, y0: torch.Tensor | None
 ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
-    g, a, y = g.contiguous(), a.contiguous(), y.contiguous()
-    y0 = y0.contiguous() if y0 is not None else None
-    _check_lane_layout(a, y, y0, "dynonet_allpole_bwd")
+    global calls
+    g, a, y, y0 = _spec.dense(g, a, y, y0)
+    _spec.demand(_ON_LANES, w=y, a=a, y0=y0)
     _lib.require_dense_cuda(g=g)
-    lanes, L = y.shape
-    gw = torch.empty_like(g)
-    ga = torch.empty_like(a)
-    gy0 = torch.empty_like(y0) if y0 is not None else None
-    if lanes:
-        st = _lib.lib().b200_allpole_bwd(lanes, L, a.shape[1], _lib.ptr(g), _lib.ptr(a), _lib.ptr(y), _lib.ptr(y0),
-                                         _lib.ptr(ga), _lib.ptr(gw), _lib.ptr(gy0), _lib.stream_ptr(y.device))
-        _lib.check(st, "b200_allpole_bwd")
-    return ga, gw, (gy0 if gy0 is not None else a.new_empty(0))
+    gw, ga = torch.empty_like(g), torch.empty_like(a)
+    gy0 = None if y0 is None else torch.empty_like(y0)
+    if y.shape[0]:
+        calls += 1
+        lanes, steps = y.shape
+        _lib.check(_lib.lib().b200_allpole_bwd(lanes, steps, a.shape[1], _lib.ptr(g), _lib.ptr(a), _lib.ptr(y),
+                                               _lib.ptr(y0), _lib.ptr(ga), _lib.ptr(gw), _lib.ptr(gy0),
+                                               _lib.stream_ptr(y.device)), "b200_allpole_bwd")
+    return ga, gw, (a.new_empty(0) if gy0 is None else gy0)
 
 
 @_allpole_bwd_op.register_fake
 def _(g, a, y, y0):
-    gy0 = torch.empty_like(y0) if y0 is not None else a.new_empty(0)
-    return torch.empty_like(a), torch.empty_like(g), gy0
+    return torch.empty_like(a), torch.empty_like(g), (a.new_empty(0) if y0 is None else torch.empty_like(y0))
 
 
-def _allpole_setup(ctx, inputs, output):
-    a, w, y0 = inputs
+def _remember(ctx, inputs, output):
+    a, _, y0 = inputs
     ctx.save_for_backward(a, output, y0)
 
 
-def _allpole_backward(ctx, g):
+def _adjoint(ctx, g):
     a, y, y0 = ctx.saved_tensors
-    grad_a, grad_w, grad_y0 = _allpole_bwd_op(g, a, y, y0)
-    return grad_a, grad_w, (grad_y0 if y0 is not None else None)
+    ga, gw, gy0 = _allpole_bwd_op(g, a, y, y0)
+    return ga, gw, (None if y0 is None else gy0)
 
 
-_allpole_op.register_autograd(_allpole_backward, setup_context=_allpole_setup)
+_allpole_op.register_autograd(_adjoint, setup_context=_remember)
 
 
 def run(a: torch.Tensor, w: torch.Tensor, y0: torch.Tensor | None) -> torch.Tensor:
     """Run the filter bank; differentiable in ``a``, ``w`` and ``y0``.
 
-    ``a [..., na]`` and ``y0 [..., na]`` broadcast over the leading dims of ``w [..., L]``; the
-    broadcast is materialised here, outside the op, so autograd folds lane gradients back.
+    ``a [..., na]`` and ``y0 [..., na]`` broadcast over the leading dims of ``w [..., L]``; they are
+    spread onto lanes here, outside the op, so autograd folds lane gradients back.
     """
-    lead, L, na = w.shape[:-1], w.shape[-1], a.shape[-1]
-    a_lane = a.broadcast_to(lead + (na,)).reshape(-1, na)
-    w_flat = w.reshape(-1, L)
-    y0_lane = y0.broadcast_to(lead + (na,)).reshape(-1, na) if y0 is not None else None
-    return _allpole_op(a_lane, w_flat, y0_lane).reshape(w.shape)
+    rows_w, rows_a, rows_y0 = _spec.lanes(w, 1, a, y0)
+    return _allpole_op(rows_a, rows_w, rows_y0).reshape(w.shape)

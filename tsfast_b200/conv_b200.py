@@ -13,64 +13,63 @@ from __future__ import annotations
 
 import torch
 
-from . import _lib
+from . import _lib, _spec
 
-__all__ = ["supports", "run"]
+__all__ = ["supports", "run", "calls"]
+
+calls = 0  # launches through this module since import (the drop-in tests read it)
+
+_WIDTH = {"K": (2, 8)}
+_F32 = (torch.float32,)
+
+
+def _contract(weight_dims):
+    return _spec.Contract(
+        op="mamba_conv_silu",
+        tensors=(_spec.Tensor("x", ("B", "L", "D")), _spec.Tensor("weight", weight_dims),
+                 _spec.Tensor("tail", ("B", "D", "Km1")), _spec.Tensor("bias", ("D",), optional=True)),
+        dtypes=_F32, ranges=_WIDTH)
+
+
+_PUBLIC = _contract(("D", 1, "K"))  # the module's depthwise Conv1d weight
+_OP = _contract(("D", "K"))         # what the ops take
+
+
+def _window_mismatch(weight, tail) -> str | None:
+    if tail.shape[-1] != weight.shape[-1] - 1:
+        return f"tail carries {tail.shape[-1]} steps, a width-{weight.shape[-1]} window needs {weight.shape[-1] - 1}"
+    return None
 
 
 def supports(x, tail, weight, bias) -> str | None:
     """Reason these tensors cannot be handled, or None when they can."""
-    if not torch.cuda.is_available():
-        return "CUDA not available"
-    tensors = {"x": x, "tail": tail, "weight": weight}
-    if bias is not None:
-        tensors["bias"] = bias
-    for name, tt in tensors.items():
-        if tt.device.type != "cuda":
-            return f"{name} not on CUDA"
-        if tt.dtype != torch.float32:
-            return f"needs float32, got {name}={tt.dtype}"
-    if x.dim() != 3:
-        return f"x must be [B, L, D], got {x.dim()} dims"
-    B, L, D = x.shape
-    if weight.dim() != 3 or weight.shape[0] != D or weight.shape[1] != 1:
-        return f"weight.shape {tuple(weight.shape)} is not depthwise [D, 1, K] for D={D}"
-    K = weight.shape[-1]
-    if not 2 <= K <= 8:
-        return f"kernel width {K} outside the supported range [2, 8]"
-    if tuple(tail.shape) != (B, D, K - 1):
-        return f"tail.shape {tuple(tail.shape)} != {(B, D, K - 1)}"
-    if bias is not None and tuple(bias.shape) != (D,):
-        return f"bias.shape {tuple(bias.shape)} != {(D,)}"
-    return None
+    return _spec.explain(_PUBLIC, x=x, weight=weight, tail=tail, bias=bias) or _window_mismatch(weight, tail)
 
 
-def _channel_last(x):
-    """x with unit channel stride (a copy only if the view is strided along channels)."""
+def _unit_channel_stride(x):
+    """``x`` itself when its channels are adjacent in memory, else a dense copy."""
     return x if x.shape[-1] == 1 or x.stride(-1) == 1 else x.contiguous()
 
 
-def _check(x, tail, w, bias, name):
-    if x.dim() != 3 or w.dim() != 2 or w.shape[0] != x.shape[2] or not 2 <= w.shape[1] <= 8:
-        raise RuntimeError(f"b200scan::{name}: expected x [B,L,D] and weight [D,K], 2<=K<=8, got "
-                           f"{tuple(x.shape)} and {tuple(w.shape)}")
-    for t in (x, tail, w, bias):
-        if t is not None and (t.dtype != torch.float32 or t.device.type != "cuda"):
-            raise RuntimeError(f"b200scan::{name}: needs float32 CUDA tensors")
+def _guard(x, tail, weight, bias, suffix=""):
+    why = _spec.explain(_OP, x=x, weight=weight, tail=tail, bias=bias) or _window_mismatch(weight, tail)
+    if why is not None:
+        raise RuntimeError(f"b200scan::mamba_conv_silu{suffix}: {why}")
 
 
 @torch.library.custom_op("b200scan::mamba_conv_silu", mutates_args=())
 def _conv_silu_op(x: torch.Tensor, tail: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None) -> torch.Tensor:
-    x = _channel_last(x)
-    tail, weight = tail.contiguous(), weight.contiguous()
-    bias = bias.contiguous() if bias is not None else None
-    _check(x, tail, weight, bias, "mamba_conv_silu")
-    B, L, D = x.shape
-    out = torch.empty(B, L, D, device=x.device, dtype=x.dtype)
+    global calls
+    x = _unit_channel_stride(x)
+    tail, weight, bias = _spec.dense(tail, weight, bias)
+    _guard(x, tail, weight, bias)
+    rows, steps, chans = x.shape
+    out = torch.empty(rows, steps, chans, device=x.device, dtype=x.dtype)
     if out.numel():
-        st = _lib.lib().b200_conv_silu_fwd(B, L, D, weight.shape[1], _lib.ptr(x), x.stride(0), x.stride(1), _lib.ptr(tail),
-                                           _lib.ptr(weight), _lib.ptr(bias), _lib.ptr(out), _lib.stream_ptr(x.device))
-        _lib.check(st, "b200_conv_silu_fwd")
+        calls += 1
+        _lib.check(_lib.lib().b200_conv_silu_fwd(rows, steps, chans, weight.shape[1], _lib.ptr(x), x.stride(0), x.stride(1),
+                                                 _lib.ptr(tail), _lib.ptr(weight), _lib.ptr(bias), _lib.ptr(out),
+                                                 _lib.stream_ptr(x.device)), "b200_conv_silu_fwd")
     return out
 
 
@@ -83,44 +82,43 @@ def _(x, tail, weight, bias):
 def _conv_silu_bwd_op(
     gy: torch.Tensor, x: torch.Tensor, tail: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None
 ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
-    x = _channel_last(x)
-    gy, tail, weight = gy.contiguous(), tail.contiguous(), weight.contiguous()
-    bias = bias.contiguous() if bias is not None else None
-    _check(x, tail, weight, bias, "mamba_conv_silu_bwd")
-    B, L, D = x.shape
-    K = weight.shape[1]
-    gx = torch.empty(B, L, D, device=x.device, dtype=x.dtype)
-    gtail = torch.zeros_like(tail)
-    gw = torch.zeros_like(weight)
-    gb = torch.zeros_like(bias) if bias is not None else None
+    global calls
+    x = _unit_channel_stride(x)
+    gy, tail, weight, bias = _spec.dense(gy, tail, weight, bias)
+    _guard(x, tail, weight, bias, "_bwd")
+    rows, steps, chans = x.shape
+    gx = torch.empty(rows, steps, chans, device=x.device, dtype=x.dtype)
+    gtail, gw = torch.zeros_like(tail), torch.zeros_like(weight)
+    gb = None if bias is None else torch.zeros_like(bias)
     if gx.numel():
+        calls += 1
         L_ = _lib.lib()
-        ws = _lib.workspace(L_.b200_conv_silu_bwd_workspace_bytes(B, L, D, K), x.device)
-        st = L_.b200_conv_silu_bwd(B, L, D, K, _lib.ptr(gy), _lib.ptr(x), x.stride(0), x.stride(1), _lib.ptr(tail),
-                                   _lib.ptr(weight), _lib.ptr(bias), _lib.ptr(gx), _lib.ptr(gtail), _lib.ptr(gw),
-                                   _lib.ptr(gb), _lib.ptr(ws), ws.numel(), _lib.stream_ptr(x.device))
-        _lib.check(st, "b200_conv_silu_bwd")
-    return gx, gtail, gw, (gb if gb is not None else gx.new_empty(0))
+        width = weight.shape[1]
+        ws = _lib.workspace(L_.b200_conv_silu_bwd_workspace_bytes(rows, steps, chans, width), x.device)
+        _lib.check(L_.b200_conv_silu_bwd(rows, steps, chans, width, _lib.ptr(gy), _lib.ptr(x), x.stride(0), x.stride(1),
+                                         _lib.ptr(tail), _lib.ptr(weight), _lib.ptr(bias), _lib.ptr(gx), _lib.ptr(gtail),
+                                         _lib.ptr(gw), _lib.ptr(gb), _lib.ptr(ws), ws.numel(), _lib.stream_ptr(x.device)),
+                   "b200_conv_silu_bwd")
+    return gx, gtail, gw, (gx.new_empty(0) if gb is None else gb)
 
 
 @_conv_silu_bwd_op.register_fake
 def _(gy, x, tail, weight, bias):
-    gb = torch.empty_like(bias) if bias is not None else gy.new_empty(0)
-    return torch.empty(x.shape, device=x.device, dtype=x.dtype), torch.empty_like(tail), torch.empty_like(weight), gb
+    return (torch.empty(x.shape, device=x.device, dtype=x.dtype), torch.empty_like(tail), torch.empty_like(weight),
+            (gy.new_empty(0) if bias is None else torch.empty_like(bias)))
 
 
-def _conv_setup(ctx, inputs, output):
-    x, tail, weight, bias = inputs
-    ctx.save_for_backward(x, tail, weight, bias)
+def _remember(ctx, inputs, output):
+    ctx.save_for_backward(*inputs)
 
 
-def _conv_backward(ctx, gy):
+def _adjoint(ctx, gy):
     x, tail, weight, bias = ctx.saved_tensors
-    gx, g_tail, gw, gb = _conv_silu_bwd_op(gy, x, tail, weight, bias)
-    return gx, g_tail, gw, (gb if bias is not None else None)
+    gx, gtail, gw, gb = _conv_silu_bwd_op(gy, x, tail, weight, bias)
+    return gx, gtail, gw, (None if bias is None else gb)
 
 
-_conv_silu_op.register_autograd(_conv_backward, setup_context=_conv_setup)
+_conv_silu_op.register_autograd(_adjoint, setup_context=_remember)
 
 
 def run(x, tail, weight, bias):

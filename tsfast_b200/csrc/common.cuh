@@ -139,11 +139,11 @@ __device__ __forceinline__ void st_release(unsigned int* p, unsigned int v) {
     asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
-// Poll a look-back flag until it is non-zero or the poll limit runs out (returns 0 then).
-__device__ __forceinline__ unsigned int wait_flag(const unsigned int* p) {
+// Poll a look-back flag until it is non-zero or `limit` polls have passed (returns 0 then).
+__device__ __forceinline__ unsigned int wait_flag(const unsigned int* p, int limit) {
     unsigned int f = ld_acquire(p);
     int spins = 0;
-    while (f == 0u && spins < kSpinLimit) {
+    while (f == 0u && spins < limit) {
         __nanosleep(40);
         f = ld_acquire(p);
         ++spins;

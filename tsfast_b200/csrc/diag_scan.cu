@@ -17,20 +17,22 @@
 // Scan: three levels over the monoid of affine maps (A, B): x -> A*x + B:
 //   1. each thread folds its TS steps sequentially in registers,
 //   2. warp 0 folds the W per-warp aggregates through shared memory,
-//   3. tiles are chained along time by decoupled look-back: a tile publishes its aggregate
-//      (flag 1), walks back over predecessors folding aggregates until it meets an inclusive
-//      state (flag 2), then publishes its own inclusive state.
+//   3. tiles are chained along time by look-back over a FIXED window: every kAnchor-th time
+//      tile is an anchor.  An anchor publishes only its inclusive state (flag 2), every other
+//      tile only its aggregate (flag 1).  A tile walks back over its predecessors folding
+//      their aggregates until it reaches the nearest anchor, waits for that anchor's inclusive
+//      state and stops.  Which values a tile folds, and in which order, therefore depends on
+//      its position alone and never on timing: two launches on the same input give the same
+//      bits.  The serial chain along one lane group is one hand-over per anchor.
 // Ticket order is time-major and every CTA works through its tickets in increasing order, so
 // the unfinished tile with the smallest ticket is always being worked on and depends only on
 // finished tiles: the chain cannot deadlock, and the bounded wait in wait_flag() can only run
-// out if the GPU itself stalls.
+// out if the GPU itself stalls (or, in the wait test, when a tile is told not to publish).
 //
 // The adjoint is the same scan in reversed time (logical step s <-> t = L-1-s) over
 // (conj(a_{t+1}), g_t), with the epilogue producing gv = G, glam and gx0.  For S1 the per-lane
 // sum glam = sum_t G_t conj(x_{t-1}) is reduced deterministically: per-tile partials go to the
 // workspace and the tile that finishes last adds them in time order.
-#include <stdlib.h>
-
 #include "common.cuh"
 
 namespace b200 {
@@ -53,7 +55,12 @@ struct DiagArgs {
     void* aggB;
     void* incl;
     void* part;  // [C*M*N]  (S1 backward)
+    int spin_limit;       // polls of one flag before a wait gives up
+    long long mute_tile;  // tile that publishes nothing (-1: none); only the bounded-wait test sets it
 };
+
+// Every kAnchor-th time tile hands over an inclusive state; the tiles between hand over aggregates.
+constexpr int kAnchor = 4;
 
 // cp.async of one pack (4, 8 or 16 bytes) from global to shared memory.
 template <int BYTES>
@@ -285,13 +292,15 @@ __global__ void __launch_bounds__(32 * W, MINB) diag_scan_kernel(const DiagArgs 
             const long long tile = k;  // k == (c*M + m)*J + j by construction
             const long long stride = p.M * p.J;  // tiles between consecutive time tiles of one lane group
             const bool has_next = tc.c + 1 < p.C;
+            const bool anchor = (tc.c % kAnchor) == 0;
+            const bool muted = tile == p.mute_tile;
             P xin = zeros;
             if (tc.c == 0) {
                 if constexpr (!BWD) {
                     if (x0 != nullptr && lane_ok) xin = *reinterpret_cast<const P*>(x0 + m * N + n0);
                 }
             } else {
-                if (has_next) {
+                if (has_next && !anchor && !muted) {  // successors fold this tile's aggregate
                     P ta, tb;
 #pragma unroll
                     for (int q = 0; q < V; ++q) {
@@ -304,7 +313,7 @@ __global__ void __launch_bounds__(32 * W, MINB) diag_scan_kernel(const DiagArgs 
                     __syncwarp();
                     if (lid == 0) st_release(p.flags + tile, 1u);
                 }
-                // look back: xin = fa * X + fb, X the state at the end of tile pt
+                // look back to the nearest anchor: xin = fa * X + fb, X the anchor's inclusive state
                 E fa[V], fb[V];
 #pragma unroll
                 for (int q = 0; q < V; ++q) {
@@ -313,15 +322,15 @@ __global__ void __launch_bounds__(32 * W, MINB) diag_scan_kernel(const DiagArgs 
                 }
                 long long pt = tile - stride;
                 for (long long cc = tc.c - 1; cc >= 0; --cc, pt -= stride) {
-                    const unsigned int f = wait_flag(p.flags + pt);
-                    if (f == 2u) {
+                    const unsigned int f = wait_flag(p.flags + pt, p.spin_limit);
+                    if (f == 0u) {  // gave up: flag the launch, keep going with what we have
+                        atomicExch(&p.hdr->error, (unsigned int)B200_ERR_TIMEOUT);
+                        break;
+                    }
+                    if ((cc % kAnchor) == 0) {  // anchors only ever publish flag 2
                         const P X = ld_cg(static_cast<const P*>(p.incl) + pt * 32 + lid);
 #pragma unroll
                         for (int q = 0; q < V; ++q) fb[q] = O::fma(fa[q], X.e[q], fb[q]);
-                        break;
-                    }
-                    if (f == 0u) {  // gave up: flag the launch, keep going with what we have
-                        atomicExch(&p.hdr->error, (unsigned int)B200_ERR_TIMEOUT);
                         break;
                     }
                     const P a = ld_cg(static_cast<const P*>(p.aggA) + pt * 32 + lid);
@@ -335,7 +344,7 @@ __global__ void __launch_bounds__(32 * W, MINB) diag_scan_kernel(const DiagArgs 
 #pragma unroll
                 for (int q = 0; q < V; ++q) xin.e[q] = fb[q];
             }
-            if (has_next) {
+            if (has_next && anchor && !muted) {
                 P ti;
 #pragma unroll
                 for (int q = 0; q < V; ++q) ti.e[q] = O::fma(pa[q], xin.e[q], pb[q]);
@@ -974,7 +983,7 @@ static int dispatch_stream(int dtype, int V, const DiagArgs& a, cudaStream_t st)
 // Streaming needs enough chains to fill the GPU.  Returns the vector width to stream with, or 0
 // to use the look-back kernel: the widest V the pointers allow that leaves at least 1.5 chains
 // per SM, else the widest that leaves one per SM.
-static int stream_v(int dtype, long long M, long long N, uintptr_t ptr_or) {
+static int stream_v(int dtype, long long M, long long N, uintptr_t ptr_or, int vcap = 0) {
     const size_t esz = dtype == B200_C64 ? 8 : 4;
     const long long sms = sm_count();
     int vmax = 1;
@@ -982,10 +991,7 @@ static int stream_v(int dtype, long long M, long long N, uintptr_t ptr_or) {
         if (N % V != 0 || (ptr_or % (esz * V)) != 0) break;
         vmax = V;
     }
-    if (const char* f = getenv("B200SCAN_DIAG_V")) {  // tuning aid: cap the width
-        const int v = atoi(f);
-        if (v >= 1 && v <= vmax && (v & (v - 1)) == 0) vmax = v;
-    }
+    if (vcap >= 1 && vcap <= vmax && (vcap & (vcap - 1)) == 0) vmax = vcap;  // b200_diag_probe only
     for (int pass = 0; pass < 2; ++pass) {
         for (int V = vmax; V >= 1; V /= 2) {
             const long long chains = M * ((N + 32 * V - 1) / (32 * V));
@@ -1010,9 +1016,18 @@ static int dispatch(int dtype, const DiagArgs& a, const DiagPlan& pl, cudaStream
     }
 }
 
+// What the regular entry points never change: kernel choice left to the shape, full vector width,
+// the one-second poll limit, every tile publishing.  b200_diag_probe passes other values.
+struct RunOpts {
+    int mode = 0;                 // 0 by shape, 1 look-back tiles, 2 streaming chains
+    int vcap = 0;                 // cap on the vector width of the streaming kernel (0: none)
+    int spin_limit = kSpinLimit;  // polls of one look-back flag
+    long long mute_tile = -1;     // look-back tile that publishes nothing
+};
+
 static int run(int dtype, bool vary, bool bwd, long long M, long long L, long long N, const void* coef,
                const void* val, const void* xsrc, const void* x0, void* out, void* gcoef, void* gx0,
-               void* ws, size_t ws_bytes, void* stream, bool tiles_only = false) {
+               void* ws, size_t ws_bytes, void* stream, const RunOpts& opt = RunOpts()) {
     if (dtype != B200_F32 && dtype != B200_C64) return B200_ERR_ARG;
     if (M < 0 || L < 0 || N < 0) return B200_ERR_ARG;
     if (M == 0 || L == 0 || N == 0) return B200_OK;
@@ -1040,12 +1055,11 @@ static int run(int dtype, bool vary, bool bwd, long long M, long long L, long lo
     a.L = L;
     a.N = N;
     a.hdr = reinterpret_cast<WsHeader*>(base);
+    a.spin_limit = opt.spin_limit > 0 ? opt.spin_limit : 1;
+    a.mute_tile = opt.mute_tile;
 
-    int mode = tiles_only ? 1 : 0;  // 0 auto, 1 look-back tiles, 2 streaming chains (tuning aid)
-    if (!tiles_only) {
-        if (const char* f = getenv("B200SCAN_DIAG_MODE")) mode = atoi(f);
-    }
-    const int sv = mode == 1 ? 0 : stream_v(dtype, M, N, por);
+    const int mode = opt.mode;
+    const int sv = mode == 1 ? 0 : stream_v(dtype, M, N, por, opt.vcap);
     if (sv > 0 || mode == 2) {
         const int V = sv > 0 ? sv : choose_v(dtype, N, por);
         if (cudaMemsetAsync(base, 0, sizeof(WsHeader), st) != cudaSuccess) return B200_ERR_LAUNCH;
@@ -1110,12 +1124,36 @@ int b200_diag_fwd_static(int dtype, int64_t M, int64_t L, int64_t N, const void*
     if (dtype != B200_F32 && dtype != B200_C64) return B200_ERR_ARG;
     if (M < 0 || L < 0 || N < 0) return B200_ERR_ARG;
     if (M == 0 || L == 0 || N == 0) return B200_OK;
+    if (!lam || !v || !out) return B200_ERR_ARG;  // before any CUDA call, like the other entry points
     if (b200::workspace_bytes(dtype, false, false, M, L, N) > b200::kStaticScratchBytes) return B200_ERR_UNSUPPORTED;
     int rc = B200_OK;
     void* scratch = b200::static_scratch_addr(&rc);
     if (rc != B200_OK) return rc;
+    b200::RunOpts opt;
+    opt.mode = 1;  // the look-back kernel is the one whose state lives in the array
     return b200::run(dtype, false, false, M, L, N, lam, v, nullptr, x0, out, nullptr, nullptr, scratch,
-                     b200::kStaticScratchBytes, stream, /*tiles_only=*/true);
+                     b200::kStaticScratchBytes, stream, opt);
+}
+
+int b200_diag_static_status(void* stream) {
+    int rc = B200_OK;
+    void* scratch = b200::static_scratch_addr(&rc);
+    if (rc != B200_OK) return rc;
+    return b200_workspace_status(scratch, stream);
+}
+
+int b200_diag_probe(int mode, int vcap, int spin_limit, int64_t mute_tile, int dtype, int varying, int backward,
+                    int64_t M, int64_t L, int64_t N, const void* lam, const void* val, const void* xsrc,
+                    const void* x0, void* out, void* glam, void* gx0, void* workspace, size_t workspace_bytes,
+                    void* stream) {
+    if (mode < 0 || mode > 2 || spin_limit < 0) return B200_ERR_ARG;
+    b200::RunOpts opt;
+    opt.mode = mode;
+    opt.vcap = vcap;
+    if (spin_limit > 0) opt.spin_limit = spin_limit;
+    opt.mute_tile = mute_tile;
+    return b200::run(dtype, varying != 0, backward != 0, M, L, N, lam, val, xsrc, x0, out, glam, gx0, workspace,
+                     workspace_bytes, stream, opt);
 }
 
 size_t b200_diag_workspace_bytes(int dtype, int backward, int64_t M, int64_t L, int64_t N) {

@@ -7,80 +7,64 @@ Drop-in for the reference's ``tsfast/models/architectures/mamba/mamba_triton.py`
 ``backend_c.py``): the same ``supports(draw, A, Bt, Ct, u, z, Dp, h0)`` / ``run(...)`` protocol and
 the same three custom ops (inference, training with state checkpoints, backward) with fake
 implementations, under the ``b200scan`` namespace.  ``run`` is differentiable in all eight inputs
-and in ``h_last``.  The kernels are ``b200_mamba_fwd`` / ``b200_mamba_bwd`` of ``libb200scan.so``;
-the checkpoint interval (8 steps, as in the reference) is the library's: ``b200_mamba_chk_interval()``.
+and in ``h_last``.  The kernels are ``b200_mamba_fwd`` / ``b200_mamba_bwd`` of ``libb200scan.so``.
+The training op's third output holds the states the adjoint restarts from, one per
+``b200_mamba_chk_interval()`` steps; its shape is this library's choice (the interface only asks
+that the fake implementation agrees with the real one).
 """
 
 from __future__ import annotations
 
+import functools
+
 import torch
 
-from . import _lib
+from . import _lib, _spec
 
-__all__ = ["supports", "run"]
+__all__ = ["supports", "run", "calls"]
 
-_MAX_N = 128
-_FAKE_CHK = 8  # checkpoint interval assumed by the fake (shape-only) implementations; checked against the library
+calls = 0  # launches through this module since import (the drop-in tests read it)
 
-
-def _chk_interval() -> int:
-    k = int(_lib.lib().b200_mamba_chk_interval())
-    if k != _FAKE_CHK:
-        raise RuntimeError(f"libb200scan checkpoints every {k} steps, this module was written for {_FAKE_CHK}")
-    return k
+_CONTRACT = _spec.Contract(
+    op="mamba_scan",
+    tensors=(_spec.Tensor("draw", ("B", "L", "D")), _spec.Tensor("A", ("D", "N")), _spec.Tensor("Bt", ("B", "L", "N")),
+             _spec.Tensor("Ct", ("B", "L", "N")), _spec.Tensor("u", ("B", "L", "D")), _spec.Tensor("z", ("B", "L", "D")),
+             _spec.Tensor("Dp", ("D",)), _spec.Tensor("h0", ("B", "D", "N"), optional=True)),
+    dtypes=(torch.float32,), ranges={"N": (1, 128)})
+_NAMES = ("draw", "A", "Bt", "Ct", "u", "z", "Dp", "h0")
 
 
 def supports(draw, A, Bt, Ct, u, z, Dp, h0) -> str | None:
     """Reason these tensors cannot be handled, or None when they can."""
-    if not torch.cuda.is_available():
-        return "CUDA not available"
-    tensors = {"draw": draw, "A": A, "Bt": Bt, "Ct": Ct, "u": u, "z": z, "Dp": Dp}
-    if h0 is not None:
-        tensors["h0"] = h0
-    for name, tt in tensors.items():
-        if tt.device.type != "cuda":
-            return f"{name} not on CUDA"
-        if tt.dtype != torch.float32:
-            return f"needs float32, got {name}={tt.dtype}"
-    if draw.dim() != 3:
-        return f"draw must be [B, L, D], got {draw.dim()} dims"
-    B, L, D = draw.shape
-    N = A.shape[-1]
-    if tuple(A.shape) != (D, N):
-        return f"A.shape {tuple(A.shape)} incompatible with draw {tuple(draw.shape)}"
-    if not 1 <= N <= _MAX_N:
-        return f"d_state={N} outside the supported range [1, {_MAX_N}]"
-    if tuple(u.shape) != (B, L, D) or tuple(z.shape) != (B, L, D):
-        return f"u/z shapes {tuple(u.shape)}/{tuple(z.shape)} != {(B, L, D)}"
-    if tuple(Bt.shape) != (B, L, N) or tuple(Ct.shape) != (B, L, N):
-        return f"Bt/Ct shapes {tuple(Bt.shape)}/{tuple(Ct.shape)} != {(B, L, N)}"
-    if tuple(Dp.shape) != (D,):
-        return f"Dp.shape {tuple(Dp.shape)} != {(D,)}"
-    if h0 is not None and tuple(h0.shape) != (B, D, N):
-        return f"h0.shape {tuple(h0.shape)} != {(B, D, N)}"
-    return None
+    return _spec.explain(_CONTRACT, **dict(zip(_NAMES, (draw, A, Bt, Ct, u, z, Dp, h0))))
 
 
-def _contig(*ts):
-    return [t.contiguous() if t is not None else None for t in ts]
+@functools.lru_cache(maxsize=None)
+def _interval() -> int:
+    """Steps between two stored states (a property of the loaded library)."""
+    return int(_lib.lib().b200_mamba_chk_interval())
 
 
-def _forward(draw, A, Bt, Ct, u, z, Dp, h0, store_chk: bool):
-    reason = supports(draw, A, Bt, Ct, u, z, Dp, h0)
-    if reason is not None:
-        raise RuntimeError(f"b200scan::mamba_scan: {reason}")
-    B, L, D = draw.shape
-    N = A.shape[-1]
+def _slots(steps: int) -> int:
+    return -(-steps // _interval())
+
+
+def _launch_forward(args, keep_states: bool):
+    global calls
+    args = _spec.dense(*args)
+    _spec.demand(_CONTRACT, **dict(zip(_NAMES, args)))
+    draw, A = args[0], args[1]
+    rows, steps, chans = draw.shape
+    n = A.shape[1]
     out = torch.empty_like(draw)
-    h_last = torch.empty(B, D, N, device=draw.device, dtype=draw.dtype)
-    chk = None
-    if store_chk:
-        chk = torch.empty(B, -(-L // _chk_interval()), D, N, device=draw.device, dtype=draw.dtype)
-    if B and D:
-        st = _lib.lib().b200_mamba_fwd(B, L, D, N, *(map(_lib.ptr, (draw, A, Bt, Ct, u, z, Dp, h0, out, h_last, chk))),
-                                       _lib.stream_ptr(draw.device))
-        _lib.check(st, "b200_mamba_fwd")
-    return out, h_last, chk
+    h_last = draw.new_empty(rows, chans, n)
+    states = draw.new_empty(rows, _slots(steps), chans, n) if keep_states else None
+    if rows and chans:
+        calls += 1
+        rc = _lib.lib().b200_mamba_fwd(rows, steps, chans, n, *(_lib.ptr(t) for t in args), _lib.ptr(out),
+                                       _lib.ptr(h_last), _lib.ptr(states), _lib.stream_ptr(draw.device))
+        _lib.check(rc, "b200_mamba_fwd")
+    return out, h_last, states
 
 
 @torch.library.custom_op("b200scan::mamba_scan", mutates_args=())
@@ -88,7 +72,7 @@ def _scan_op(
     draw: torch.Tensor, A: torch.Tensor, Bt: torch.Tensor, Ct: torch.Tensor, u: torch.Tensor, z: torch.Tensor,
     Dp: torch.Tensor, h0: torch.Tensor | None,
 ) -> tuple[torch.Tensor, torch.Tensor]:
-    out, h_last, _ = _forward(*_contig(draw, A, Bt, Ct, u, z, Dp, h0), store_chk=False)
+    out, h_last, _ = _launch_forward((draw, A, Bt, Ct, u, z, Dp, h0), keep_states=False)
     return out, h_last
 
 
@@ -97,27 +81,19 @@ def _scan_train_op(
     draw: torch.Tensor, A: torch.Tensor, Bt: torch.Tensor, Ct: torch.Tensor, u: torch.Tensor, z: torch.Tensor,
     Dp: torch.Tensor, h0: torch.Tensor | None,
 ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
-    return _forward(*_contig(draw, A, Bt, Ct, u, z, Dp, h0), store_chk=True)
-
-
-def _fake_outs(draw, A, with_chk: bool):
-    B, L, D = draw.shape
-    N = A.shape[-1]
-    out = torch.empty_like(draw)
-    h_last = draw.new_empty(B, D, N)
-    if not with_chk:
-        return out, h_last
-    return out, h_last, draw.new_empty(B, -(-L // _FAKE_CHK), D, N)
+    return _launch_forward((draw, A, Bt, Ct, u, z, Dp, h0), keep_states=True)
 
 
 @_scan_op.register_fake
 def _(draw, A, Bt, Ct, u, z, Dp, h0):
-    return _fake_outs(draw, A, with_chk=False)
+    return torch.empty_like(draw), draw.new_empty(draw.shape[0], draw.shape[2], A.shape[1])
 
 
 @_scan_train_op.register_fake
 def _(draw, A, Bt, Ct, u, z, Dp, h0):
-    return _fake_outs(draw, A, with_chk=True)
+    rows, steps, chans = draw.shape
+    return (torch.empty_like(draw), draw.new_empty(rows, chans, A.shape[1]),
+            draw.new_empty(rows, _slots(steps), chans, A.shape[1]))
 
 
 @torch.library.custom_op("b200scan::mamba_scan_bwd", mutates_args=())
@@ -126,56 +102,60 @@ def _scan_bwd_op(
     Bt: torch.Tensor, Ct: torch.Tensor, u: torch.Tensor, z: torch.Tensor, Dp: torch.Tensor, h0: torch.Tensor | None,
 ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor,
            torch.Tensor]:
-    gout, ghlast, chk, draw, A, Bt, Ct, u, z, Dp, h0 = _contig(gout, ghlast, chk, draw, A, Bt, Ct, u, z, Dp, h0)
+    global calls
+    gout, ghlast, chk, draw, A, Bt, Ct, u, z, Dp, h0 = _spec.dense(gout, ghlast, chk, draw, A, Bt, Ct, u, z, Dp, h0)
     _lib.require_dense_cuda(gout=gout, ghlast=ghlast, chk=chk)
-    B, L, D = draw.shape
-    N = A.shape[-1]
-    new = lambda *s: torch.empty(*s, device=draw.device, dtype=draw.dtype)  # noqa: E731
-    gdraw, gu, gz = torch.empty_like(draw), torch.empty_like(draw), torch.empty_like(draw)
-    gA, gBt, gCt, gDp = new(D, N), new(B, L, N), new(B, L, N), new(D)
-    gh0 = new(B, D, N) if h0 is not None else None
-    if B and D:
+    rows, steps, chans = draw.shape
+    n = A.shape[1]
+    grads = {"draw": torch.empty_like(draw), "A": draw.new_empty(chans, n), "Bt": draw.new_empty(rows, steps, n),
+             "Ct": draw.new_empty(rows, steps, n), "u": torch.empty_like(draw), "z": torch.empty_like(draw),
+             "Dp": draw.new_empty(chans), "h0": None if h0 is None else draw.new_empty(rows, chans, n)}
+    if rows and chans:
+        calls += 1
         L_ = _lib.lib()
-        ws = _lib.workspace(L_.b200_mamba_bwd_workspace_bytes(B, L, D, N), draw.device)
-        st = L_.b200_mamba_bwd(
-            B, L, D, N,
-            *(map(_lib.ptr, (draw, A, Bt, Ct, u, z, Dp, h0, chk, gout, ghlast, gdraw, gA, gBt, gCt, gu, gz, gDp, gh0, ws))),
-            ws.numel(), _lib.stream_ptr(draw.device))
-        _lib.check(st, "b200_mamba_bwd")
-    else:
-        gA.zero_(), gDp.zero_()
-    return gdraw, gA, gBt, gCt, gu, gz, gDp, (gh0 if gh0 is not None else gout.new_empty(0))
+        ws = _lib.workspace(L_.b200_mamba_bwd_workspace_bytes(rows, steps, chans, n), draw.device)
+        inputs = (draw, A, Bt, Ct, u, z, Dp, h0, chk, gout, ghlast)
+        outputs = tuple(grads[k] for k in ("draw", "A", "Bt", "Ct", "u", "z", "Dp", "h0"))
+        rc = L_.b200_mamba_bwd(rows, steps, chans, n, *(_lib.ptr(t) for t in inputs + outputs), _lib.ptr(ws), ws.numel(),
+                               _lib.stream_ptr(draw.device))
+        _lib.check(rc, "b200_mamba_bwd")
+    else:  # empty batch or no channels: the sums over (batch, time) are empty
+        grads["A"].zero_()
+        grads["Dp"].zero_()
+    if grads["h0"] is None:
+        grads["h0"] = gout.new_empty(0)
+    return tuple(grads[k] for k in ("draw", "A", "Bt", "Ct", "u", "z", "Dp", "h0"))
 
 
 @_scan_bwd_op.register_fake
 def _(gout, ghlast, chk, draw, A, Bt, Ct, u, z, Dp, h0):
-    B, L, D = draw.shape
-    N = A.shape[-1]
-    return (torch.empty_like(draw), draw.new_empty(D, N), draw.new_empty(B, L, N), draw.new_empty(B, L, N),
-            torch.empty_like(draw), torch.empty_like(draw), draw.new_empty(D),
-            (draw.new_empty(B, D, N) if h0 is not None else draw.new_empty(0)))
+    rows, steps, chans = draw.shape
+    n = A.shape[1]
+    per_step_n = draw.new_empty(rows, steps, n)
+    return (torch.empty_like(draw), torch.empty_like(A), per_step_n, torch.empty_like(per_step_n), torch.empty_like(draw),
+            torch.empty_like(draw), torch.empty_like(Dp), (draw.new_empty(0) if h0 is None else draw.new_empty(rows, chans, n)))
 
 
-def _scan_setup(ctx, inputs, output):
-    draw, A, Bt, Ct, u, z, Dp, h0 = inputs
-    ctx.save_for_backward(draw, A, Bt, Ct, u, z, Dp, h0, output[2])
+def _remember(ctx, inputs, output):
+    ctx.save_for_backward(*inputs, output[2])
 
 
-def _scan_backward(ctx, gout, ghlast, gchk):
-    draw, A, Bt, Ct, u, z, Dp, h0, chk = ctx.saved_tensors
-    if gout is None:
+def _adjoint(ctx, gout, ghlast, _gstates):
+    *inputs, states = ctx.saved_tensors
+    draw, h0 = inputs[0], inputs[7]
+    if gout is None:  # only h_last was used downstream
         gout = torch.zeros_like(draw)
-    gdraw, gA, gBt, gCt, gu, gz, gDp, gh0 = _scan_bwd_op(gout, ghlast, chk, draw, A, Bt, Ct, u, z, Dp, h0)
-    return gdraw, gA, gBt, gCt, gu, gz, gDp, (gh0 if h0 is not None else None)
+    grads = _scan_bwd_op(gout, ghlast, states, *inputs)
+    return grads[:7] + ((None if h0 is None else grads[7]),)
 
 
-_scan_train_op.register_autograd(_scan_backward, setup_context=_scan_setup)
+_scan_train_op.register_autograd(_adjoint, setup_context=_remember)
 
 
 def run(draw, A, Bt, Ct, u, z, Dp, h0):
     """Fused section → ``(out [B, L, D], h_last [B, D, N])``; differentiable in every input and in ``h_last``."""
-    inputs = (draw, A, Bt, Ct, u, z, Dp) + ((h0,) if h0 is not None else ())
-    if not torch.is_grad_enabled() or not any(t.requires_grad for t in inputs):
+    needs_grad = torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in (draw, A, Bt, Ct, u, z, Dp, h0))
+    if not needs_grad:
         return _scan_op(draw, A, Bt, Ct, u, z, Dp, h0)
-    out, h_last, _chk = _scan_train_op(draw, A, Bt, Ct, u, z, Dp, h0)
+    out, h_last, _states = _scan_train_op(draw, A, Bt, Ct, u, z, Dp, h0)
     return out, h_last

@@ -10,116 +10,96 @@ functions with the same argument meaning,
 
 each a forward/backward pair of ``torch.library`` custom ops (namespace ``b200scan``, so they
 can live beside the reference's ``tsfast::`` ops) with fake implementations and the analytic
-reverse-scan adjoint registered for autograd.  Broadcasting is materialised outside the ops,
-exactly as the reference does, so plain autograd folds lane gradients back onto broadcast
-shapes.  Only ``(lam, out, x0)`` are saved for backward.  There is no fallback path: the ops
-call the CUDA library and raise if it is missing or the tensors are not float32/complex64 CUDA.
+reverse-scan adjoint registered for autograd.  Both functions and all four ops are generated from
+one description of a scan (``_Kind``); broadcasting is spread onto the lane layout outside the ops
+(``_on_lanes``), so plain autograd folds lane gradients back onto broadcast shapes.  Only
+``(lam, out, x0)`` are saved for backward, as the interface prescribes.  There is no fallback path:
+the ops call the CUDA library and raise if it is missing or the tensors are not float32/complex64
+CUDA tensors.
 """
 
 from __future__ import annotations
 
 import torch
 
-from .scan_backends import diagonal_b200, selective_b200
+from . import _spec
+from .scan_backends import _common
 
 __all__ = ["diagonal_recurrence", "selective_recurrence"]
 
 
-def _dense(*ts):
-    return [None if t is None else t.contiguous() for t in ts]
+class _Kind:
+    """One diagonal scan: its launcher and whether the coefficient carries a time axis."""
+
+    def __init__(self, name: str, launcher: _common.Scan, per_step: bool):
+        self.name, self.launcher, self.per_step = name, launcher, per_step
+
+    def guard(self, lam, v, x0, suffix=""):
+        why = self.launcher.why_not(lam, v, x0)
+        if why is not None:
+            raise RuntimeError(f"b200scan::{self.name}{suffix}: {why}")
+
+    def state_like(self, lam):
+        """An empty tensor shaped like one state ``[rows, n]`` of this scan."""
+        return torch.empty_like(lam[:, 0] if self.per_step else lam)
+
+    def build(self):
+        kind = self
+
+        @torch.library.custom_op(f"b200scan::{kind.name}", mutates_args=())
+        def fwd(lam: torch.Tensor, v: torch.Tensor, x0: torch.Tensor | None) -> torch.Tensor:
+            lam, v, x0 = _spec.dense(lam, v, x0)
+            kind.guard(lam, v, x0)
+            return kind.launcher.forward(lam, v, x0)
+
+        @fwd.register_fake
+        def _(lam, v, x0):
+            return torch.empty_like(v)
+
+        @torch.library.custom_op(f"b200scan::{kind.name}_bwd", mutates_args=())
+        def bwd(g: torch.Tensor, lam: torch.Tensor, out: torch.Tensor,
+                x0: torch.Tensor | None) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+            g, lam, out, x0 = _spec.dense(g, lam, out, x0)
+            kind.guard(lam, g, x0, "_bwd")
+            return kind.launcher.backward(g, lam, out, x0)
+
+        @bwd.register_fake
+        def _(g, lam, out, x0):
+            return torch.empty_like(lam), torch.empty_like(g), (lam.new_empty(0) if x0 is None else kind.state_like(lam))
+
+        def remember(ctx, inputs, output):
+            lam, _, x0 = inputs
+            ctx.save_for_backward(lam, output, x0)
+
+        def adjoint(ctx, g):
+            lam, out, x0 = ctx.saved_tensors
+            glam, gv, gx0 = bwd(g, lam, out, x0)
+            return glam, gv, (None if x0 is None else gx0)
+
+        fwd.register_autograd(adjoint, setup_context=remember)
+        return fwd, bwd
 
 
-def _require(mod, lam, v, x0, name):
-    reason = mod.supports(lam, v, x0)
-    if reason is not None:
-        raise RuntimeError(f"b200scan::{name}: {reason}")
+_DIAG = _Kind("scan_diagonal", _common.DIAGONAL, per_step=False)
+_SEL = _Kind("scan_selective", _common.SELECTIVE, per_step=True)
+_scan_diagonal_op, _scan_diagonal_bwd_op = _DIAG.build()
+_scan_selective_op, _scan_selective_bwd_op = _SEL.build()
 
 
-# ------------------------------------------------------------------------- S1 ops
-@torch.library.custom_op("b200scan::scan_diagonal", mutates_args=())
-def _scan_diagonal_op(lam: torch.Tensor, v: torch.Tensor, x0: torch.Tensor | None) -> torch.Tensor:
-    lam, v, x0 = _dense(lam, v, x0)
-    _require(diagonal_b200, lam, v, x0, "scan_diagonal")
-    return diagonal_b200.forward(lam, v, x0)
+def _on_lanes(kind: _Kind, lam, v, x0):
+    """Spread ``lam``, ``v``, ``x0`` over their common leading dims and flatten those to rows."""
+    coef_shape = tuple(lam.shape) if kind.per_step else tuple(lam.shape[:-1]) + (1, lam.shape[-1])
+    full = torch.broadcast_shapes(coef_shape, v.shape)
+    lead, steps, n = tuple(full[:-2]), full[-2], full[-1]
+    rows_v = v.expand(full).reshape(-1, steps, n)
+    if kind.per_step:
+        rows_lam = lam.expand(full).reshape(-1, steps, n)
+    else:
+        rows_lam = lam.expand(lead + (n,)).reshape(-1, n)
+    rows_x0 = None if x0 is None else x0.expand(lead + (n,)).reshape(-1, n)
+    return rows_lam, rows_v, rows_x0, full
 
 
-@_scan_diagonal_op.register_fake
-def _(lam, v, x0):
-    return torch.empty_like(v)
-
-
-@torch.library.custom_op("b200scan::scan_diagonal_bwd", mutates_args=())
-def _scan_diagonal_bwd_op(
-    g: torch.Tensor, lam: torch.Tensor, out: torch.Tensor, x0: torch.Tensor | None
-) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
-    g, lam, out, x0 = _dense(g, lam, out, x0)
-    _require(diagonal_b200, lam, g, x0, "scan_diagonal_bwd")
-    return diagonal_b200.backward(g, lam, out, x0)
-
-
-@_scan_diagonal_bwd_op.register_fake
-def _(g, lam, out, x0):
-    gx0 = torch.empty_like(lam) if x0 is not None else lam.new_empty(0)
-    return torch.empty_like(lam), torch.empty_like(g), gx0
-
-
-def _diag_setup(ctx, inputs, output):
-    lam, v, x0 = inputs
-    ctx.save_for_backward(lam, output, x0)
-
-
-def _diag_backward(ctx, g):
-    lam, out, x0 = ctx.saved_tensors
-    glam, gv, gx0 = _scan_diagonal_bwd_op(g, lam, out, x0)
-    return glam, gv, (gx0 if x0 is not None else None)
-
-
-_scan_diagonal_op.register_autograd(_diag_backward, setup_context=_diag_setup)
-
-
-# ------------------------------------------------------------------------- S2 ops
-@torch.library.custom_op("b200scan::scan_selective", mutates_args=())
-def _scan_selective_op(lam: torch.Tensor, v: torch.Tensor, x0: torch.Tensor | None) -> torch.Tensor:
-    lam, v, x0 = _dense(lam, v, x0)
-    _require(selective_b200, lam, v, x0, "scan_selective")
-    return selective_b200.forward(lam, v, x0)
-
-
-@_scan_selective_op.register_fake
-def _(lam, v, x0):
-    return torch.empty_like(v)
-
-
-@torch.library.custom_op("b200scan::scan_selective_bwd", mutates_args=())
-def _scan_selective_bwd_op(
-    g: torch.Tensor, lam: torch.Tensor, out: torch.Tensor, x0: torch.Tensor | None
-) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
-    g, lam, out, x0 = _dense(g, lam, out, x0)
-    _require(selective_b200, lam, g, x0, "scan_selective_bwd")
-    return selective_b200.backward(g, lam, out, x0)
-
-
-@_scan_selective_bwd_op.register_fake
-def _(g, lam, out, x0):
-    gx0 = torch.empty_like(lam[..., 0, :]) if x0 is not None else lam.new_empty(0)
-    return torch.empty_like(lam), torch.empty_like(g), gx0
-
-
-def _sel_setup(ctx, inputs, output):
-    lam, v, x0 = inputs
-    ctx.save_for_backward(lam, output, x0)
-
-
-def _sel_backward(ctx, g):
-    lam, out, x0 = ctx.saved_tensors
-    glam, gv, gx0 = _scan_selective_bwd_op(g, lam, out, x0)
-    return glam, gv, (gx0 if x0 is not None else None)
-
-
-_scan_selective_op.register_autograd(_sel_backward, setup_context=_sel_setup)
-
-
-# ------------------------------------------------------------------------- public API
 def diagonal_recurrence(lam: torch.Tensor, v: torch.Tensor, x0: torch.Tensor | None = None) -> torch.Tensor:
     """``x_t = lam * x_{t-1} + v_t`` with constant diagonal ``lam``; returns ``x_1..x_L``.
 
@@ -128,12 +108,8 @@ def diagonal_recurrence(lam: torch.Tensor, v: torch.Tensor, x0: torch.Tensor | N
         v: input sequence ``[..., L, n]`` (float32 or complex64, CUDA).
         x0: initial state ``[..., n]``; zeros if None.
     """
-    out_shape = torch.broadcast_shapes(lam.unsqueeze(-2).shape, v.shape)
-    bdims, L, n = out_shape[:-2], out_shape[-2], out_shape[-1]
-    lam_lane = lam.broadcast_to(bdims + (n,)).reshape(-1, n)
-    v_flat = v.broadcast_to(out_shape).reshape(-1, L, n)
-    x0_lane = None if x0 is None else x0.broadcast_to(bdims + (n,)).reshape(-1, n)
-    return _scan_diagonal_op(lam_lane, v_flat, x0_lane).reshape(out_shape)
+    rows_lam, rows_v, rows_x0, full = _on_lanes(_DIAG, lam, v, x0)
+    return _scan_diagonal_op(rows_lam, rows_v, rows_x0).reshape(full)
 
 
 def selective_recurrence(lam: torch.Tensor, v: torch.Tensor, x0: torch.Tensor | None = None) -> torch.Tensor:
@@ -144,9 +120,5 @@ def selective_recurrence(lam: torch.Tensor, v: torch.Tensor, x0: torch.Tensor | 
         v: input sequence ``[..., L, n]`` (float32 or complex64, CUDA).
         x0: initial state ``[..., n]``; zeros if None.
     """
-    out_shape = torch.broadcast_shapes(lam.shape, v.shape)
-    bdims, L, n = out_shape[:-2], out_shape[-2], out_shape[-1]
-    lam3 = lam.broadcast_to(out_shape).reshape(-1, L, n)
-    v3 = v.broadcast_to(out_shape).reshape(-1, L, n)
-    x03 = None if x0 is None else x0.broadcast_to(bdims + (n,)).reshape(-1, n)
-    return _scan_selective_op(lam3, v3, x03).reshape(out_shape)
+    rows_lam, rows_v, rows_x0, full = _on_lanes(_SEL, lam, v, x0)
+    return _scan_selective_op(rows_lam, rows_v, rows_x0).reshape(full)

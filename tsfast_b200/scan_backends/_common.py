@@ -1,72 +1,64 @@
-"""Shared launch plumbing of the two diagonal-scan backends."""
+"""Launch path shared by the S1 (constant coefficient) and S2 (per-step coefficient) backends.
+
+Both scans run the same two CUDA kernels; they differ in the coefficient's shape and in the entry
+points' names (``b200_diag_*`` / ``b200_sel_*``).  ``Scan`` binds one of the two and offers the
+three calls tsfast's backend protocol asks for.
+"""
 
 from __future__ import annotations
 
 import torch
 
-from .. import _lib
+from .. import _lib, _spec, status
 
-# Workspace of the most recent launch per op, kept so tests can read the device status word.
-LAST_WS: dict[str, torch.Tensor] = {}
-
-
-def _supports(lam, v, x0, varying: bool) -> str | None:
-    if not torch.cuda.is_available():
-        return "CUDA not available"
-    if v.device.type != "cuda" or lam.device.type != "cuda":
-        return "inputs not on CUDA"
-    if v.dtype not in (torch.float32, torch.complex64):
-        return f"dtype {v.dtype} unsupported (need float32 or complex64)"
-    if lam.dtype != v.dtype:
-        return f"lam dtype {lam.dtype} != v dtype {v.dtype}"
-    if x0 is not None and (x0.dtype != v.dtype or x0.device != v.device):
-        return f"x0 must match v in dtype and device, got {x0.dtype} on {x0.device}"
-    if v.dim() != 3:
-        return f"v must be [rows, L, n] on the lane layout, got {v.dim()} dims"
-    M, L, N = v.shape
-    if varying:
-        if lam.shape != v.shape:
-            return f"lam.shape {tuple(lam.shape)} != v.shape {tuple(v.shape)}"
-    elif tuple(lam.shape) != (M, N):
-        return f"lam.shape {tuple(lam.shape)} != {(M, N)}"
-    if x0 is not None and tuple(x0.shape) != (M, N):
-        return f"x0.shape {tuple(x0.shape)} != {(M, N)}"
-    return None
+_DTYPES = (torch.float32, torch.complex64)
 
 
-def run_forward(op: str, lam, v, x0):
-    L_ = _lib.lib()
-    _lib.require_dense_cuda(lam=lam, v=v, x0=x0)
-    M, L, N = v.shape
-    tag = _lib.dtype_tag(v.dtype)
-    out = torch.empty_like(v)
-    if out.numel() == 0:
+class Scan:
+    """One of the two diagonal scans on the lane layout ``[rows, L, n]``."""
+
+    def __init__(self, entry: str, per_step: bool):
+        self.entry = entry
+        coef = ("R", "L", "N") if per_step else ("R", "N")
+        self.contract = _spec.Contract(
+            op=f"scan_{'selective' if per_step else 'diagonal'}",
+            tensors=(_spec.Tensor("v", ("R", "L", "N")), _spec.Tensor("lam", coef),
+                     _spec.Tensor("x0", ("R", "N"), optional=True)),
+            dtypes=_DTYPES)
+
+    def why_not(self, lam, v, x0) -> str | None:
+        return _spec.explain(self.contract, v=v, lam=lam, x0=x0)
+
+    def _call(self, which: str, backward: bool, shape, dtype, device, *pointers):
+        L_ = _lib.lib()
+        rows, steps, n = shape
+        tag = _lib.dtype_tag(dtype)
+        ws = _lib.workspace(getattr(L_, f"b200_{self.entry}_workspace_bytes")(tag, int(backward), rows, steps, n), device)
+        rc = getattr(L_, f"b200_{self.entry}_{which}")(tag, rows, steps, n, *pointers, _lib.ptr(ws), ws.numel(),
+                                                        _lib.stream_ptr(device))
+        _lib.check(rc, f"b200_{self.entry}_{which}")
+        status.remember(ws)
+
+    def forward(self, lam, v, x0):
+        _lib.require_dense_cuda(lam=lam, v=v, x0=x0)
+        out = torch.empty_like(v)
+        if out.numel():
+            self._call("fwd", False, v.shape, v.dtype, v.device, _lib.ptr(lam), _lib.ptr(v), _lib.ptr(x0), _lib.ptr(out))
         return out
-    ws = _lib.workspace(getattr(L_, f"b200_{op}_workspace_bytes")(tag, 0, M, L, N), v.device)
-    st = getattr(L_, f"b200_{op}_fwd")(tag, M, L, N, _lib.ptr(lam), _lib.ptr(v), _lib.ptr(x0), _lib.ptr(out),
-                                        _lib.ptr(ws), ws.numel(), _lib.stream_ptr(v.device))
-    _lib.check(st, f"b200_{op}_fwd")
-    LAST_WS[op] = ws
-    return out
+
+    def backward(self, g, lam, out, x0):
+        _lib.require_dense_cuda(g=g, lam=lam, out=out, x0=x0)
+        glam, gv = torch.empty_like(lam), torch.empty_like(out)
+        gx0 = None if x0 is None else torch.empty_like(x0)
+        if out.numel():
+            self._call("bwd", True, out.shape, out.dtype, out.device, _lib.ptr(g), _lib.ptr(lam), _lib.ptr(out),
+                       _lib.ptr(x0), _lib.ptr(glam), _lib.ptr(gv), _lib.ptr(gx0))
+        else:  # nothing to scan: the sums over time are empty
+            glam.zero_()
+            if gx0 is not None:
+                gx0.zero_()
+        return glam, gv, (lam.new_empty(0) if gx0 is None else gx0)
 
 
-def run_backward(op: str, g, lam, out, x0):
-    L_ = _lib.lib()
-    _lib.require_dense_cuda(g=g, lam=lam, out=out, x0=x0)
-    M, L, N = out.shape
-    tag = _lib.dtype_tag(out.dtype)
-    glam = torch.empty_like(lam)
-    gv = torch.empty_like(out)
-    gx0 = torch.empty_like(x0) if x0 is not None else None
-    if out.numel() == 0:
-        glam.zero_()
-        if gx0 is not None:
-            gx0.zero_()
-        return glam, gv, (gx0 if gx0 is not None else lam.new_empty(0))
-    ws = _lib.workspace(getattr(L_, f"b200_{op}_workspace_bytes")(tag, 1, M, L, N), out.device)
-    st = getattr(L_, f"b200_{op}_bwd")(tag, M, L, N, _lib.ptr(g), _lib.ptr(lam), _lib.ptr(out), _lib.ptr(x0),
-                                        _lib.ptr(glam), _lib.ptr(gv), _lib.ptr(gx0), _lib.ptr(ws), ws.numel(),
-                                        _lib.stream_ptr(out.device))
-    _lib.check(st, f"b200_{op}_bwd")
-    LAST_WS[op] = ws
-    return glam, gv, (gx0 if gx0 is not None else lam.new_empty(0))
+DIAGONAL = Scan("diag", per_step=False)
+SELECTIVE = Scan("sel", per_step=True)

@@ -8,23 +8,27 @@ same ``supports`` / ``forward`` / ``backward`` protocol on the lane layout (``la
 
 from __future__ import annotations
 
-import torch
+from ._common import DIAGONAL as _scan
 
-from . import _common
+__all__ = ["supports", "forward", "backward", "calls"]
 
-__all__ = ["supports", "forward", "backward"]
+calls = 0  # launches through this module since import (the drop-in tests read it)
 
 
-def supports(lam: torch.Tensor, v: torch.Tensor, x0: torch.Tensor | None) -> str | None:
+def supports(lam, v, x0):
     """Reason these tensors cannot be handled, or None when they can."""
-    return _common._supports(lam, v, x0, varying=False)
+    return _scan.why_not(lam, v, x0)
 
 
-def forward(lam: torch.Tensor, v: torch.Tensor, x0: torch.Tensor | None) -> torch.Tensor:
+def forward(lam, v, x0):
     """States ``x_1..x_L`` as ``[M, L, N]``."""
-    return _common.run_forward("diag", lam, v, x0)
+    global calls
+    calls += 1
+    return _scan.forward(lam, v, x0)
 
 
 def backward(g, lam, out, x0):
     """Adjoint sweep → ``(glam [M,N], gv [M,L,N], gx0 [M,N])``; ``gx0`` is empty when ``x0 is None``."""
-    return _common.run_backward("diag", g, lam, out, x0)
+    global calls
+    calls += 1
+    return _scan.backward(g, lam, out, x0)

@@ -1,29 +1,34 @@
 """B200 backend of the time-varying diagonal scan ``x_t = lam_t * x_{t-1} + v_t``.
 
-Drop-in for the reference's ``scan_backends/selective_triton.py`` / ``selective_c.py`` modules
-(``lam, v [B,L,N]``, ``x0 [B,N] | None``, contiguous).  Unlike those it also takes complex64,
-with the conjugation rules of the reference's doubling scan (``_core/scan.py:173-195``).
+Drop-in for the reference's ``scan_backends/selective_triton.py`` / ``selective_c.py`` modules:
+same ``supports`` / ``forward`` / ``backward`` protocol on the lane layout (``lam``, ``v``
+``[B,L,N]``, ``x0 [B,N] | None``, contiguous).  Unlike the reference's CUDA kernel (float32 only)
+this one also takes complex64.  Entry points: ``b200_sel_fwd`` / ``b200_sel_bwd``.
 """
 
 from __future__ import annotations
 
-import torch
+from ._common import SELECTIVE as _scan
 
-from . import _common
+__all__ = ["supports", "forward", "backward", "calls"]
 
-__all__ = ["supports", "forward", "backward"]
+calls = 0  # launches through this module since import (the drop-in tests read it)
 
 
-def supports(lam: torch.Tensor, v: torch.Tensor, x0: torch.Tensor | None) -> str | None:
+def supports(lam, v, x0):
     """Reason these tensors cannot be handled, or None when they can."""
-    return _common._supports(lam, v, x0, varying=True)
+    return _scan.why_not(lam, v, x0)
 
 
-def forward(lam: torch.Tensor, v: torch.Tensor, x0: torch.Tensor | None) -> torch.Tensor:
+def forward(lam, v, x0):
     """States ``x_1..x_L`` as ``[B, L, N]``."""
-    return _common.run_forward("sel", lam, v, x0)
+    global calls
+    calls += 1
+    return _scan.forward(lam, v, x0)
 
 
 def backward(g, lam, out, x0):
     """Adjoint sweep → ``(glam [B,L,N], gv [B,L,N], gx0 [B,N])``; ``gx0`` is empty when ``x0 is None``."""
-    return _common.run_backward("sel", g, lam, out, x0)
+    global calls
+    calls += 1
+    return _scan.backward(g, lam, out, x0)
