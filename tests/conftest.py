@@ -35,8 +35,9 @@ def import_tsfast_models():
     ref = reference_checkout()
     if ref is None:
         pytest.skip("no tsfast checkout (run `python oracle/make_ref.py <checkout>` or set TSFAST_CHECKOUT)")
-    os.environ.setdefault("CXX", "/usr/bin/g++")
-    os.environ.setdefault("CC", "/usr/bin/gcc")
+    for var, exe in (("CXX", "/usr/bin/g++"), ("CC", "/usr/bin/gcc")):
+        if os.path.exists(exe):
+            os.environ[var] = exe
     if str(ref) not in sys.path:
         sys.path.insert(0, str(ref))
     try:

@@ -1,17 +1,14 @@
-"""Host-side mirror of tsfast's LRU caller stack, running its recurrence on the B200 scan.
+"""TEST HELPERS: small stand-ins for tsfast's caller modules, for machines without a tsfast copy.
 
-tsfast's ``LRU`` / ``LRUBlock`` / ``DeepLRU`` (``tsfast/models/architectures/lru.py:16-234``) are the
-modules that call ``diagonal_recurrence``.  With tsfast importable they are used unchanged after
-``tsfast_b200.install()``.  This file exists for machines where tsfast is not installed (the
-benchmark's full-model configuration and its tests): the same layer stack with the same parameter
-names and shapes, so a tsfast ``DeepLRU.state_dict()`` loads into ``DeepLRU`` here and both
-produce the same numbers, but with the recurrence hard-wired to
-``tsfast_b200.diagonal_recurrence`` (no backend switch, no CPU path).
+The drop-in is shown with tsfast's own modules (``test_dropin_gpu.py``).  These mirrors exist so the
+golden fixtures taken from tsfast's ``DeepLRU``, ``LinearDynamicalOperator`` and ``DynoNet`` can also be
+replayed where tsfast is not importable: the same layer stacks with the same parameter names and
+shapes (a tsfast ``state_dict`` loads unchanged) with the recurrences hard-wired to this package's
+ops.  They are not part of the product.
 
-Layer maths (Orvieto et al. 2023; tsfast ``lru.py:79-110``, ``_core/scan.py:272-313``):
+Layer maths of the LRU mirror (Orvieto et al. 2023; tsfast ``lru.py:79-110``, ``_core/scan.py:272-313``):
 ``lam = exp(-exp(nu_log) + i exp(theta_log))``; ``v_k = exp(gamma_log) * (B u_k)`` with complex
-``B = B_re + i B_im``; ``x_k = lam x_{k-1} + v_k``; ``y_k = Re(C x_k) + D u_k``.  The two boundary
-projections are single real GEMMs against interleaved weights, so the complex views are free.
+``B = B_re + i B_im``; ``x_k = lam x_{k-1} + v_k``; ``y_k = Re(C x_k) + D u_k``.
 """
 
 from __future__ import annotations
@@ -22,9 +19,8 @@ import torch
 import torch.nn.functional as F
 from torch import nn
 
-from .scan import diagonal_recurrence
-
-__all__ = ["LRU", "LRUBlock", "DeepLRU", "project_in", "project_out"]
+from tsfast_b200.dynonet_b200 import _MAX_NA, _NB_SIZES, linear_block
+from tsfast_b200.scan import diagonal_recurrence
 
 
 def project_in(u: torch.Tensor, w_re: torch.Tensor, w_im: torch.Tensor) -> torch.Tensor:
@@ -118,3 +114,76 @@ class DeepLRU(nn.Module):
             carried.append(s_new)
         y = self.decoder(h)
         return (y, carried) if self.return_state else y
+
+
+class LinearDynamicalOperator(nn.Module):
+    """MIMO bank of rational transfer functions ``B(q)/A(q)``, one SISO filter per (output, input)
+    pair, outputs summed over inputs: the mirror of tsfast's module of the same name
+    (``dynonet/core.py:144-254``) with the whole forward in one kernel."""
+
+    def __init__(self, in_channels: int, out_channels: int, nb: int = 8, na: int = 2):
+        super().__init__()
+        if not 1 <= na <= _MAX_NA or not 1 <= nb <= _NB_SIZES[-1]:
+            raise ValueError(f"the fused block needs 1 <= na <= {_MAX_NA} and 1 <= nb <= {_NB_SIZES[-1]}")
+        self.in_channels, self.out_channels, self.nb, self.na = in_channels, out_channels, nb, na
+        self.b_coeff = nn.Parameter(torch.randn(out_channels, in_channels, nb) * 0.01)
+        self.a_coeff = nn.Parameter(torch.zeros(out_channels, in_channels, na))
+
+    @property
+    def n_pairs(self) -> int:
+        return self.in_channels * self.out_channels
+
+    def forward(self, u: torch.Tensor, state: dict | None = None, return_state: bool = False):
+        y, new_state = linear_block(u, self.b_coeff, self.a_coeff, state)
+        return (y, new_state) if return_state else y
+
+
+class _PointwiseMLP(nn.Module):
+    """The static nonlinearity F: an MLP on the feature axis with the parameter names of tsfast's
+    ``SeqLinear`` (``tsfast/models/_core/layers.py:16-60``: ``lin.<k>.0`` hidden layers, last ``lin.<n>``)."""
+
+    def __init__(self, input_size: int, output_size: int, hidden_size: int, hidden_layer: int, act: type[nn.Module]):
+        super().__init__()
+        if hidden_layer < 1:
+            self.lin = nn.Linear(input_size, output_size)
+        else:
+            sizes = [input_size] + [hidden_size] * hidden_layer
+            self.lin = nn.Sequential(*[nn.Sequential(nn.Linear(i, o), act()) for i, o in zip(sizes[:-1], sizes[1:])],
+                                     nn.Linear(hidden_size, output_size))
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return self.lin(x)
+
+
+class DynoNet(nn.Module):
+    """``G1 -> F -> G2`` with an optional parallel linear path ``G_lin`` (Forgione & Piga 2021), the
+    mirror of tsfast's ``DynoNet`` (``dynonet/core.py:257-346``) on the fused G-blocks: same
+    constructor arguments, submodule names (``g1``, ``f``, ``g2``, ``g_lin``) and state protocol
+    (``forward(u, state=None)`` with ``{"g1": ..., "g2": ..., "lin": ...}``)."""
+
+    def __init__(self, input_size: int, output_size: int, n_channels: int = 8, nb: int = 8, na: int = 2,
+                 hidden_size: int = 32, hidden_layers: int = 1, act: type[nn.Module] = nn.Tanh, bypass: bool = True,
+                 return_state: bool = False):
+        super().__init__()
+        self.return_state = return_state
+        self.g1 = LinearDynamicalOperator(input_size, n_channels, nb, na)
+        self.f = _PointwiseMLP(n_channels, n_channels, hidden_size, hidden_layers, act)
+        self.g2 = LinearDynamicalOperator(n_channels, output_size, nb, na)
+        self.g_lin = LinearDynamicalOperator(input_size, output_size, nb, na) if bypass else None
+
+    def forward(self, u: torch.Tensor, state: dict | None = None):
+        match state:
+            case None:
+                s1 = s2 = s_lin = None
+            case dict():
+                s1, s2, s_lin = state.get("g1"), state.get("g2"), state.get("lin")
+            case _:
+                raise TypeError(f"expected state dict, got {type(state)}")
+        y1, s1 = self.g1(u, state=s1, return_state=True)
+        y, s2 = self.g2(self.f(y1), state=s2, return_state=True)
+        new_state = {"g1": s1, "g2": s2}
+        if self.g_lin is not None:
+            y_lin, s_lin = self.g_lin(u, state=s_lin, return_state=True)
+            y = y + y_lin
+            new_state["lin"] = s_lin
+        return (y, new_state) if self.return_state else y

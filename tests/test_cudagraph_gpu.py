@@ -47,7 +47,7 @@ def test_graph_capture_of_raw_entry_points_replays_on_new_data():
 def test_make_graphed_callables_on_the_lru_stack():
     """Forward AND backward of a DeepLRU captured by torch.cuda.make_graphed_callables (what
     GraphedStatefulModel uses) match the eager module."""
-    from tsfast_b200.lru_model import DeepLRU
+    from mirrors import DeepLRU
 
     torch.manual_seed(1)
     eager = DeepLRU(2, 3, d_model=16, d_state=32, n_layers=2, r_min=0.5, r_max=0.95, max_phase=1.0).cuda()

@@ -32,23 +32,50 @@ def _backend(kind):
     return diagonal_b200 if kind == "diag" else selective_b200
 
 
-def _status_ok(kind):
+_MODE = {"auto": 0, "lookback": 1, "stream": 2}
+
+
+def _probe(kind, backward, mode, lam, val, xsrc, x0, spin_limit=0, mute_tile=-1):
+    """One launch through b200_diag_probe with this test's own workspace; returns (outputs, device status)."""
     from tsfast_b200 import _lib
-    from tsfast_b200.scan_backends import _common
 
-    ws = _common.LAST_WS.get(kind)
-    assert ws is None or _lib.last_status(ws) == 0
+    L_ = _lib.lib()
+    M, L, N = val.shape
+    tag = _lib.dtype_tag(val.dtype)
+    p = _lib.ptr
+    ws = _lib.workspace(getattr(L_, f"b200_{kind}_workspace_bytes")(tag, int(backward), M, L, N), val.device)
+    out = torch.empty_like(val)
+    glam = torch.empty_like(lam) if backward else None
+    gx0 = torch.empty_like(x0) if (backward and x0 is not None) else None
+    rc = L_.b200_diag_probe(_MODE[mode], 0, spin_limit, mute_tile, tag, int(kind == "sel"), int(backward), M, L, N,
+                            p(lam), p(val), p(xsrc), p(x0), p(out), p(glam), p(gx0), p(ws), ws.numel(),
+                            _lib.stream_ptr(val.device))
+    _lib.check(rc, "b200_diag_probe")
+    return (out, glam, gx0), _lib.workspace_status(ws)
 
 
-def _run(kind, lam, v, x0, g):
-    """Forward + adjoint on the lane layout; numpy in, numpy out."""
-    mod = _backend(kind)
+def _run(kind, lam, v, x0, g, mode="auto"):
+    """Forward + adjoint on the lane layout; numpy in, numpy out.  ``auto`` goes through the backend
+    module (the product path), the forced kernel modes through the probe entry point."""
     lam_d, v_d, x0_d, g_d = _dev(lam), _dev(v), _dev(x0), _dev(g)
-    assert mod.supports(lam_d, v_d, x0_d) is None
-    out = mod.forward(lam_d, v_d, x0_d)
-    _status_ok(kind)
-    glam, gv, gx0 = mod.backward(g_d, lam_d, out, x0_d)
-    _status_ok(kind)
+    if mode == "auto":
+        import tsfast_b200
+
+        mod = _backend(kind)
+        assert mod.supports(lam_d, v_d, x0_d) is None
+        tsfast_b200.track_status(True)
+        try:
+            out = mod.forward(lam_d, v_d, x0_d)
+            tsfast_b200.check_status()
+            glam, gv, gx0 = mod.backward(g_d, lam_d, out, x0_d)
+            tsfast_b200.check_status()
+        finally:
+            tsfast_b200.track_status(False)
+    else:
+        (out, _, _), st = _probe(kind, False, mode, lam_d, v_d, None, x0_d)
+        assert st == 0
+        (gv, glam, gx0), st = _probe(kind, True, mode, lam_d, g_d, out, x0_d)
+        assert st == 0
     torch.cuda.synchronize()
     return _host(out), _host(glam), _host(gv), (_host(gx0) if x0 is not None else None)
 
@@ -62,7 +89,7 @@ def _lane(kind, lam, v):
 def test_golden(kernel_mode, kind):
     for c in load_golden(kind):
         lam = _lane(kind, c.lam, c.v)
-        out, glam, gv, gx0 = _run(kind, lam, c.v, c.x0, c.g)
+        out, glam, gv, gx0 = _run(kind, lam, c.v, c.x0, c.g, kernel_mode)
         if kind == "diag" and c.lam.ndim == 1:
             glam = glam.sum(0)
         assert rel_err(out, c.ref64_out) < REL, (c.name, "out")
@@ -99,13 +126,9 @@ _SHAPES = [(32, 200, 64), (16, 200, 32), (4, 257, 8), (2, 7, 3), (3, 1, 6), (1, 
 
 
 @pytest.fixture(params=["auto", "lookback", "stream"])
-def kernel_mode(request, monkeypatch):
-    """Both kernels must pass every shape: 1 forces the look-back tiles, 2 the streaming chains."""
-    code = {"auto": None, "lookback": "1", "stream": "2"}[request.param]
-    if code is None:
-        monkeypatch.delenv("B200SCAN_DIAG_MODE", raising=False)
-    else:
-        monkeypatch.setenv("B200SCAN_DIAG_MODE", code)
+def kernel_mode(request):
+    """Both kernels must pass every shape: the look-back tiles and the streaming chains are forced
+    through b200_diag_probe, ``auto`` is the product path that picks by shape."""
     return request.param
 
 
@@ -115,7 +138,7 @@ def kernel_mode(request, monkeypatch):
 @pytest.mark.parametrize("shape", _SHAPES)
 def test_matches_oracle(oracle, kernel_mode, kind, cplx, with_x0, shape):
     lam, v, x0, g = _rand_case(kind, shape, cplx, with_x0, seed=sum(shape) * 8 + (kind == "sel") * 4 + cplx * 2 + with_x0)
-    out, glam, gv, gx0 = _run(kind, lam, v, x0, g)
+    out, glam, gv, gx0 = _run(kind, lam, v, x0, g, kernel_mode)
     fwd = oracle.diag_fwd if kind == "diag" else oracle.sel_fwd
     bwd = oracle.diag_bwd if kind == "diag" else oracle.sel_bwd
     ro = fwd(_to64(lam), _to64(v), _to64(x0))
@@ -130,13 +153,40 @@ def test_matches_oracle(oracle, kernel_mode, kind, cplx, with_x0, shape):
 
 
 @pytest.mark.parametrize("kind", ["diag", "sel"])
-def test_run_twice_bitwise_identical(kernel_mode, kind):
-    """No atomics on data: two launches on the same inputs give identical bits (incl. S1's glam)."""
-    lam, v, x0, g = _rand_case(kind, (3, 700, 96), True, True, seed=5)
-    a = _run(kind, lam, v, x0, g)
-    b = _run(kind, lam, v, x0, g)
-    for x, y in zip(a, b):
-        assert np.array_equal(x, y)
+@pytest.mark.parametrize("shape", [(3, 700, 96), (2, 3000, 40)])
+def test_run_twice_bitwise_identical(kernel_mode, kind, shape):
+    """No atomics on data and a look-back window that depends on position only: repeated launches
+    on the same inputs give identical bits (incl. S1's glam).  The look-back runs are repeated with
+    other work in flight on a second stream, which shifts tile timing without changing the fold order."""
+    lam, v, x0, g = _rand_case(kind, shape, True, True, seed=5)
+    a = _run(kind, lam, v, x0, g, kernel_mode)
+    side = torch.cuda.Stream()
+    noise = torch.empty(64 << 20, device="cuda")
+    for _ in range(3):
+        with torch.cuda.stream(side):
+            for _ in range(4):
+                noise.normal_()
+        b = _run(kind, lam, v, x0, g, kernel_mode)
+        for x, y in zip(a, b):
+            assert np.array_equal(x, y)
+    torch.cuda.synchronize()
+
+
+def test_bounded_wait_gives_up_and_reports():
+    """A look-back wait is bounded: when a tile never publishes (the probe's mute_tile), the tiles
+    after it stop polling after spin_limit polls, the launch records B200_ERR_TIMEOUT and returns;
+    the next ordinary launch on the same shape reports no error and is exact again."""
+    lam, v, x0, _ = _rand_case("sel", (2, 900, 64), False, True, seed=3)
+    lam_d, v_d, x0_d = _dev(lam), _dev(v), _dev(x0)
+    (want, _, _), st = _probe("sel", False, "lookback", lam_d, v_d, None, x0_d)
+    assert st == 0
+    # tile ids are time-major; tile 0 is the first time tile of the first lane group: an anchor
+    (_, _, _), st = _probe("sel", False, "lookback", lam_d, v_d, None, x0_d, spin_limit=64, mute_tile=0)
+    torch.cuda.synchronize()
+    assert st == 5  # B200_ERR_TIMEOUT
+    (again, _, _), st = _probe("sel", False, "lookback", lam_d, v_d, None, x0_d)
+    assert st == 0
+    assert torch.equal(again, want)
 
 
 def test_unaligned_views_take_the_scalar_path(oracle):
@@ -163,13 +213,11 @@ def test_config2_full_size_properties():
     b = torch.randn(B, L, N, device="cuda", generator=gen)
     g = torch.randn(B, L, N, device="cuda", generator=gen)
     x = mod.forward(a, b, None)
-    _status_ok("sel")
     res = x[:, 1:] - (a[:, 1:] * x[:, :-1] + b[:, 1:])
     scale = x.abs().max().item()
     assert res.abs().max().item() < 1e-5 * scale
     assert (x[:, 0] - b[:, 0]).abs().max().item() == 0.0
     glam, gv, _ = mod.backward(g, a, x, None)
-    _status_ok("sel")
     res = gv[:, :-1] - (g[:, :-1] + a[:, 1:] * gv[:, 1:])
     assert res.abs().max().item() < 1e-5 * gv.abs().max().item()
     assert (gv[:, -1] - g[:, -1]).abs().max().item() == 0.0

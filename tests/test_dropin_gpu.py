@@ -1,0 +1,206 @@
+"""The drop-in shown on a GPU with tsfast's OWN modules and its OWN test files.
+
+After ``tsfast_b200.install()`` tsfast's DeepLRU, DeepS5, DeepMamba and DynoNet (imported from the
+unmodified reference copy that ``oracle/make_ref.py`` places under ``oracle/_ref``) run on CUDA under
+``use_backend("auto")`` and are compared with the same modules under ``use_backend("reference")``
+in float64: outputs, every parameter gradient, a three-chunk stateful roll-out with gradient through
+the carried state, ``torch.compile(fullgraph=True)`` and tsfast's ``GraphedStatefulModel``.  Launch
+counters on the B200 modules prove that these kernels, not tsfast's Triton ones, were entered.
+The last test runs tsfast's hot-path test files unmodified in a child pytest with the backend
+installed from a plugin and requires that none fails.
+
+Tolerances: model outputs and parameter gradients ``max|a-b|/max|b| < 1e-3`` against the float64
+reference path, the bound tsfast's own model-level backend tests use
+(``tests/test_scan_selective_backends.py:69-95``); scan-level checks stay at ``1e-4`` elsewhere.
+"""
+
+import copy
+import json
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+from conftest import ROOT, import_tsfast_models, reference_checkout
+
+pytestmark = pytest.mark.gpu
+
+MODEL_TOL = 1e-3
+
+
+def _rel(a, b):
+    return (a.double() - b.double()).abs().max().item() / (b.double().abs().max().item() + 1e-30)
+
+
+@pytest.fixture(scope="module")
+def tsfast_installed():
+    m = import_tsfast_models()
+    import tsfast_b200
+
+    tsfast_b200.install()
+    prev = torch.backends.cuda.matmul.allow_tf32, torch.backends.cudnn.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    torch.backends.cudnn.allow_tf32 = False
+    yield m
+    torch.backends.cuda.matmul.allow_tf32, torch.backends.cudnn.allow_tf32 = prev
+    tsfast_b200.uninstall()
+
+
+def _launches():
+    from tsfast_b200 import allpole_b200, conv_b200, mamba_b200
+    from tsfast_b200.scan_backends import diagonal_b200, selective_b200
+
+    return {"diag": diagonal_b200.calls, "sel": selective_b200.calls, "ssm": mamba_b200.calls,
+            "conv": conv_b200.calls, "allpole": allpole_b200.calls}
+
+
+def _build(m, family):
+    torch.manual_seed(0)
+    if family == "lru":
+        return m.DeepLRU(3, 2, d_model=32, d_state=48, n_layers=2, return_state=True), "diag"
+    if family == "s5":
+        return m.DeepS5(3, 2, d_model=32, d_state=32, n_layers=2, return_state=True), "diag"
+    if family == "mamba":
+        return m.DeepMamba(3, 2, d_model=32, d_state=16, n_layers=2, return_state=True), "ssm"
+    return m.DynoNet(3, 2, n_channels=4, nb=4, na=2, return_state=True), "allpole"
+
+
+def _chunked(model, u, cuts):
+    """Roll the model over ``u`` in chunks, handing the state over; gradient flows through it."""
+    outs, state, lo = [], None, 0
+    for hi in list(cuts) + [u.shape[1]]:
+        y, state = model(u[:, lo:hi], state=state)
+        outs.append(y)
+        lo = hi
+    return torch.cat(outs, dim=1)
+
+
+@pytest.mark.parametrize("family", ["lru", "s5", "mamba", "dynonet"])
+def test_tsfast_models_on_b200_kernels_match_float64_reference(tsfast_installed, family):
+    m = tsfast_installed
+    from tsfast.models import use_backend
+
+    model32, counter = _build(m, family)
+    model64 = copy.deepcopy(model32).double()
+    if family == "dynonet":  # dynoNet starts with a = 0; give the poles something to do
+        for mod in (model32, model64):
+            torch.manual_seed(1)
+            with torch.no_grad():
+                for p in mod.parameters():
+                    if p.dim() == 3 and p.shape[-1] == 2:
+                        p.normal_(0, 0.2)
+    model32, model64 = model32.cuda(), model64.cuda()
+    torch.manual_seed(2)
+    u = torch.randn(4, 96, 3, device="cuda")
+    cuts = (40, 43)  # second chunk is shorter than the conv window / filter order of some models
+
+    before = _launches()[counter]
+    with use_backend("auto"):
+        got = _chunked(model32, u, cuts)
+        (got**2).mean().backward()
+    assert _launches()[counter] > before, f"the B200 {counter} backend was never entered"
+    with use_backend("reference"):
+        want = _chunked(model64, u.double(), cuts)
+        (want**2).mean().backward()
+
+    assert _rel(got, want) < MODEL_TOL
+    worst = ("", 0.0)
+    for (name, p), q in zip(model32.named_parameters(), model64.parameters()):
+        assert p.grad is not None, name
+        r = _rel(p.grad, q.grad)
+        if r > worst[1]:
+            worst = (name, r)
+    assert worst[1] < MODEL_TOL, f"{family}: worst parameter gradient {worst}"
+    with use_backend("auto"), torch.no_grad():  # inference path equals the autograd path
+        again = _chunked(model32, u, cuts)
+    assert _rel(again, got) < 1e-6
+
+
+def test_reference_preference_bypasses_b200(tsfast_installed):
+    m = tsfast_installed
+    from tsfast.models import use_backend
+
+    model, counter = _build(m, "lru")
+    model = model.cuda()
+    u = torch.randn(2, 30, 3, device="cuda")
+    before = _launches()
+    with use_backend("reference"), torch.no_grad():
+        model(u)
+    assert _launches() == before
+    with use_backend("triton"), torch.no_grad():  # the family name install() registers under
+        model(u)
+    assert _launches()[counter] > before[counter]
+
+
+@pytest.mark.parametrize("family", ["lru", "mamba"])
+def test_compile_fullgraph_through_tsfast_modules(tsfast_installed, family):
+    m = tsfast_installed
+    model, counter = _build(m, family)
+    model = model.cuda()
+    model.return_state = False
+    u = torch.randn(2, 64, 3, device="cuda")
+    eager = model(u)
+    before = _launches()[counter]
+    out = torch.compile(model, fullgraph=True)(u)
+    out.square().mean().backward()
+    assert _launches()[counter] > before
+    assert _rel(out, eager) < 1e-5
+    assert all(p.grad is not None for p in model.parameters())
+
+
+@pytest.mark.parametrize("family", ["lru", "mamba"])
+def test_graphed_stateful_model_of_tsfast(tsfast_installed, family):
+    """tsfast's own CUDA-graph wrapper (flat state bridge, make_graphed_callables) around its own
+    model, running on these kernels: replay equals eager, forward and parameter gradients."""
+    m = tsfast_installed
+    from tsfast.models._core.cudagraph import GraphedStatefulModel
+
+    model, counter = _build(m, family)
+    model = model.cuda()
+    eager = copy.deepcopy(model)
+    graphed = GraphedStatefulModel(model)
+    torch.manual_seed(5)
+    before = _launches()[counter]
+    state_g = state_e = None
+    for step in range(3):
+        u = torch.randn(4, 50, 3, device="cuda")
+        yg, state_g = graphed(u, state_g)
+        ye, state_e = eager(u, state=state_e)
+        assert _rel(yg, ye) < 1e-5, step
+        yg.square().mean().backward()
+        ye.square().mean().backward()
+        from tsfast.models._core.state import detach_state
+
+        state_g, state_e = detach_state(state_g), detach_state(state_e)
+    assert not graphed._capture_failed, "tsfast fell back to eager: the capture failed"
+    assert graphed._graphed is not None
+    assert _launches()[counter] > before
+    for (name, p), q in zip(model.named_parameters(), eager.parameters()):
+        assert _rel(p.grad, q.grad) < 1e-4, name
+
+
+def test_tsfast_own_test_files_pass_with_b200_installed(tmp_path):
+    """tsfast's hot-path test files, unmodified, in a child pytest with the backend installed."""
+    ref = reference_checkout()
+    if ref is None or not (ref / "tests" / "test_scan.py").exists():
+        pytest.skip("no reference copy with its tests (python oracle/make_ref.py <checkout>)")
+    report = tmp_path / "report.json"
+    env = dict(os.environ, B200_DROPIN_REPORT=str(report), CXX="/usr/bin/g++", CC="/usr/bin/gcc", TSFAST_AUTOTUNE_CACHE="1",
+               PYTHONPATH=os.pathsep.join([str(ref), str(ROOT), str(ROOT / "tests"), os.environ.get("PYTHONPATH", "")]))
+    files = sorted(str(p) for p in (ref / "tests").glob("test_*.py"))
+    cmd = [sys.executable, "-m", "pytest", "-q", "-x", "--no-header", "-p", "ref_plugin", "-p", "no:cacheprovider",
+           "--rootdir", str(ref), "-c", os.devnull, *files]
+    r = subprocess.run(cmd, env=env, cwd=str(ref), capture_output=True, text=True, timeout=2400)
+    tail = (r.stdout + r.stderr)[-4000:]
+    assert report.exists(), tail
+    rep = json.loads(report.read_text())
+    out_dir = ROOT / "gpurun_out"
+    if out_dir.is_dir():
+        (out_dir / "reference_tests_with_b200.json").write_text(json.dumps(rep, indent=1))
+    assert rep["failed"] == 0 and r.returncode == 0, (rep, tail)
+    assert rep["passed"] > 100
+    for slot in ("scan.diagonal", "scan.selective", "mamba.ssm", "mamba.conv", "dynonet.allpole"):
+        assert rep["launches"][slot] > 0, f"{slot}: tsfast's tests never reached the B200 module"

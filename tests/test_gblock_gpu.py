@@ -150,7 +150,7 @@ def test_gradient_through_the_new_state(warp_split):
 
 
 def test_module_mirror_loads_reference_state_dict_names():
-    from tsfast_b200.dynonet_b200 import LinearDynamicalOperator
+    from mirrors import LinearDynamicalOperator
 
     op = LinearDynamicalOperator(2, 3, nb=8, na=2).cuda()
     assert set(op.state_dict()) == {"b_coeff", "a_coeff"}
@@ -167,7 +167,7 @@ def test_dynonet_matches_reference_model():
     float64 output and parameter gradients (fixture from tsfast's DynoNet, dynonet/core.py:257-346)."""
     from pathlib import Path
 
-    from tsfast_b200.dynonet_b200 import DynoNet
+    from mirrors import DynoNet
 
     z = np.load(Path(__file__).parent / "golden" / "dynonet.npz")
     net = DynoNet(2, 1, n_channels=4, nb=8, na=2, hidden_size=16, hidden_layers=1, bypass=True)

@@ -2,7 +2,7 @@
 
 `tests/golden/deeplru.npz` holds a small reference model (float64, `use_backend("reference")`):
 parameters, input, output, carried states and every parameter gradient.  The mirror in
-`tsfast_b200.lru_model` loads that state_dict unchanged and must reproduce all of it in float32
+`tests/mirrors.py` loads that state_dict unchanged and must reproduce all of it in float32
 (bound 1e-4 relative, TF32 off as in the reference's model-level parity tests,
 tests/test_lru.py:157-170), and a chunked rollout with the carried state must equal one pass."""
 
@@ -17,7 +17,7 @@ pytestmark = pytest.mark.gpu
 
 @pytest.fixture
 def golden_model():
-    from tsfast_b200.lru_model import DeepLRU
+    from mirrors import DeepLRU
 
     torch.backends.cuda.matmul.allow_tf32 = False
     torch.backends.cudnn.allow_tf32 = False
@@ -57,7 +57,7 @@ def test_config5_shape_gradient_is_a_descent_direction():
     gradient through the whole stack matches a central finite difference along itself (5 %), and a
     data-parallel step with a small learning rate lowers the loss."""
     from tsfast_b200.dist import dp_train_step
-    from tsfast_b200.lru_model import DeepLRU
+    from mirrors import DeepLRU
 
     torch.backends.cuda.matmul.allow_tf32 = False
     torch.manual_seed(0)

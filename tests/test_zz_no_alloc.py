@@ -4,8 +4,9 @@ Some users of the library cannot allocate device memory where they call it: a fi
 estimation loop, or a process confined to a device arena its host application handed it.  For them
 the library keeps the look-back kernel's cross-tile state in a 4 MiB array of its own.  This test
 calls the entry point through the C ABI twice in a row (the second call meets the first call's
-leftovers in the shared array) and checks both results against the workspace-taking entry point,
-which the parity tests pin to the oracle; it also checks that an oversized problem is refused.
+leftovers in the shared array) and checks that both results equal, bit for bit, those of the
+workspace-taking entry point, which the parity tests pin to the oracle, and that the array's
+error word reads zero afterwards; it also checks that an oversized problem is refused.
 The file sorts last so that a run stopping at the first failure has already run everything else.
 """
 
@@ -59,9 +60,11 @@ def test_static_scratch_matches_regular_entry_point_twice(cplx):
             want = _regular(L_, tag, lam, v, x0)
             got = _static(L_, tag, lam, v, x0)
             torch.cuda.synchronize()
-            scale = want.abs().max().item()
-            # same tolerance as the parity tests: max|a-b| / max|b| < 1e-4
-            assert (got - want).abs().max().item() < 1e-4 * scale, (M, L, N, trial)
+            # both entry points run the look-back kernel on these shapes, and its fold order depends
+            # on tile position only, so the two results agree bit for bit
+            assert torch.equal(torch.view_as_real(got) if cplx else got,
+                               torch.view_as_real(want) if cplx else want), (M, L, N, trial)
+            assert L_.b200_diag_static_status(_lib.stream_ptr(v.device)) == 0
 
 
 def test_static_scratch_refuses_oversized_problem():

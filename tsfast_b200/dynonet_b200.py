@@ -10,10 +10,8 @@ never reaches memory and the per-pair outputs only when the adjoint will need th
   with tsfast's tensor layouts and state dict (``{"u": FIR tail, "x": IIR states}``).  It is
   differentiable: the adjoint is ``b200_gblock_bwd`` (the all-pole adjoint of every pair reading the
   output gradient in place, then one kernel for the numerator's input and tap gradients).
-* :class:`LinearDynamicalOperator` mirrors the reference module (same constructor, parameter names
-  and ``forward(u, state=None, return_state=False)``), so a tsfast state dict loads into it.
-* :class:`DynoNet` is the block interconnection ``G1 -> F -> G2`` (+ linear bypass) built from it,
-  with the reference's submodule and parameter names.
+* ``tsfast_b200.install(fuse_dynonet=True)`` routes tsfast's own ``LinearDynamicalOperator`` (and so
+  its ``DynoNet``) through it.
 
 float32 on CUDA, ``1 <= na <= 4`` and ``nb <= 16``; anything else raises (tsfast's own module is the
 place for other shapes: this package has no second path).
@@ -22,12 +20,11 @@ place for other shapes: this package has no second path).
 from __future__ import annotations
 
 import torch
-from torch import nn
 
 from . import _lib
 from .allpole_b200 import _allpole_bwd_op
 
-__all__ = ["linear_block", "LinearDynamicalOperator", "DynoNet", "supports"]
+__all__ = ["linear_block", "supports"]
 
 _MAX_NA = 4
 _SPLIT_BELOW = 296  # (batch row, output) warps under which the forward runs one warp per filter: 2 per SM
@@ -259,76 +256,3 @@ def linear_block(u: torch.Tensor, b_coeff: torch.Tensor, a_coeff: torch.Tensor, 
     else:
         new_tail = u.new_zeros(B, 0, I)
     return y.transpose(1, 2), {"u": new_tail, "x": x_last}
-
-
-class LinearDynamicalOperator(nn.Module):
-    """MIMO bank of rational transfer functions ``B(q)/A(q)``, one SISO filter per (output, input)
-    pair, outputs summed over inputs: the mirror of tsfast's module of the same name
-    (``dynonet/core.py:144-254``) with the whole forward in one kernel."""
-
-    def __init__(self, in_channels: int, out_channels: int, nb: int = 8, na: int = 2):
-        super().__init__()
-        if not 1 <= na <= _MAX_NA or not 1 <= nb <= _NB_SIZES[-1]:
-            raise ValueError(f"the fused block needs 1 <= na <= {_MAX_NA} and 1 <= nb <= {_NB_SIZES[-1]}")
-        self.in_channels, self.out_channels, self.nb, self.na = in_channels, out_channels, nb, na
-        self.b_coeff = nn.Parameter(torch.randn(out_channels, in_channels, nb) * 0.01)
-        self.a_coeff = nn.Parameter(torch.zeros(out_channels, in_channels, na))
-
-    @property
-    def n_pairs(self) -> int:
-        return self.in_channels * self.out_channels
-
-    def forward(self, u: torch.Tensor, state: dict | None = None, return_state: bool = False):
-        y, new_state = linear_block(u, self.b_coeff, self.a_coeff, state)
-        return (y, new_state) if return_state else y
-
-
-class _PointwiseMLP(nn.Module):
-    """The static nonlinearity F: an MLP on the feature axis with the parameter names of tsfast's
-    ``SeqLinear`` (``tsfast/models/_core/layers.py:16-60``: ``lin.<k>.0`` hidden layers, last ``lin.<n>``)."""
-
-    def __init__(self, input_size: int, output_size: int, hidden_size: int, hidden_layer: int, act: type[nn.Module]):
-        super().__init__()
-        if hidden_layer < 1:
-            self.lin = nn.Linear(input_size, output_size)
-        else:
-            sizes = [input_size] + [hidden_size] * hidden_layer
-            self.lin = nn.Sequential(*[nn.Sequential(nn.Linear(i, o), act()) for i, o in zip(sizes[:-1], sizes[1:])],
-                                     nn.Linear(hidden_size, output_size))
-
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return self.lin(x)
-
-
-class DynoNet(nn.Module):
-    """``G1 -> F -> G2`` with an optional parallel linear path ``G_lin`` (Forgione & Piga 2021), the
-    mirror of tsfast's ``DynoNet`` (``dynonet/core.py:257-346``) on the fused G-blocks: same
-    constructor arguments, submodule names (``g1``, ``f``, ``g2``, ``g_lin``) and state protocol
-    (``forward(u, state=None)`` with ``{"g1": ..., "g2": ..., "lin": ...}``)."""
-
-    def __init__(self, input_size: int, output_size: int, n_channels: int = 8, nb: int = 8, na: int = 2,
-                 hidden_size: int = 32, hidden_layers: int = 1, act: type[nn.Module] = nn.Tanh, bypass: bool = True,
-                 return_state: bool = False):
-        super().__init__()
-        self.return_state = return_state
-        self.g1 = LinearDynamicalOperator(input_size, n_channels, nb, na)
-        self.f = _PointwiseMLP(n_channels, n_channels, hidden_size, hidden_layers, act)
-        self.g2 = LinearDynamicalOperator(n_channels, output_size, nb, na)
-        self.g_lin = LinearDynamicalOperator(input_size, output_size, nb, na) if bypass else None
-
-    def forward(self, u: torch.Tensor, state: dict | None = None):
-        match state:
-            case None:
-                s1 = s2 = s_lin = None
-            case dict():
-                s1, s2, s_lin = state.get("g1"), state.get("g2"), state.get("lin")
-            case _:
-                raise TypeError(f"expected state dict, got {type(state)}")
-        y1, s1 = self.g1(u, state=s1, return_state=True)
-        y, s2 = self.g2(self.f(y1), state=s2, return_state=True)
-        new_state = {"g1": s1, "g2": s2}
-        if self.g_lin is not None:
-            y_lin, s_lin = self.g_lin(u, state=s_lin, return_state=True)
-            y = y + y_lin
-            new_state["lin"] = s_lin
-        return (y, new_state) if self.return_state else y
