@@ -42,6 +42,7 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 B, T, D = 64, 4096, 256
+C2_SHAPE = (B, T, D)
 TENSOR_BYTES = B * T * D * 4
 FWD_BYTES = 3 * TENSOR_BYTES  # a, b -> h
 BWD_BYTES = 5 * TENSOR_BYTES  # g, a, h -> ga, gb
@@ -579,9 +580,9 @@ def _workload(name, torch, dev, rank, host_buffers=True, impl="b200"):
         return torch.empty(t.shape, dtype=t.dtype, pin_memory=True).copy_(t)
 
     if name == "C2":
-        a = torch.sigmoid(rn(B, T, D) + 2.0)
-        b, g = rn(B, T, D), rn(B, T, D)
-        return dict(desc=WORKLOAD, fwd_bytes=FWD_BYTES, bwd_bytes=BWD_BYTES, elems=2 * B * T * D, rows=B, flush=False,
+        a = torch.sigmoid(rn(*C2_SHAPE) + 2.0)
+        b, g = rn(*C2_SHAPE), rn(*C2_SHAPE)
+        return dict(desc=WORKLOAD, fwd_bytes=FWD_BYTES, bwd_bytes=BWD_BYTES, elems=2 * TENSOR_BYTES // 4, rows=C2_SHAPE[0], flush=False,
                     dtype="f32", launches=2, fwd=lambda: selective_b200.forward(a, b, None),
                     bwd=lambda o: selective_b200.backward(g, a, o, None))
     if name == "C1":
@@ -933,7 +934,7 @@ def _c5_measure(torch, dist, dev, world, rank, local, barrier, steps, warmup):
                         f"({C5_SHAPE['windows'] * world} global), Adam, NCCL gradient all-reduce",
             "ms_per_step": round(ms, 3), "steps": steps, "windows_per_gpu": C5_SHAPE["windows"],
             "windows_per_s": round(C5_SHAPE["windows"] * world / (ms * 1e-3), 1),
-            "allreduce_ms": round(statistics.mean(a.elapsed_time(b) for a, b in ar), 3), "final_loss": round(float(loss), 6)}
+            "allreduce_ms": round(statistics.mean(a.elapsed_time(b) for a, b in ar), 3), "final_loss": round(float(loss.detach()), 6)}
 
 
 def _run_c5(args, torch, dist, dev, world, rank, local, barrier):

@@ -20,6 +20,20 @@ def pytest_configure(config):
     config._b200_slots = tsfast_b200.install()
 
 
+# fixtures of tsfast's conftest that open its dataset files; tests that ask for one train a Learner on
+# recorded data, which is outside the scan path (and the files are not part of the reference copy)
+_DATA_FIXTURES = {"wh_path", "pinn_var_ic_path", "hdf_files", "dls_simulation", "dls_short", "dls_prediction", "pinn_path",
+                  "orientation_path", "dls_pinn"}
+
+
+def pytest_collection_modifyitems(config, items):
+    import pytest
+
+    for item in items:
+        if _DATA_FIXTURES & set(getattr(item, "fixturenames", ())):
+            item.add_marker(pytest.mark.skip(reason="needs tsfast's dataset files (not on the scan path)"))
+
+
 def pytest_runtest_logreport(report):
     if report.when == "call" or (report.when == "setup" and report.outcome != "passed"):
         _counts[report.outcome] = _counts.get(report.outcome, 0) + 1

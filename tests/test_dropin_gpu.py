@@ -191,7 +191,7 @@ def test_tsfast_own_test_files_pass_with_b200_installed(tmp_path):
     env = dict(os.environ, B200_DROPIN_REPORT=str(report), CXX="/usr/bin/g++", CC="/usr/bin/gcc", TSFAST_AUTOTUNE_CACHE="1",
                PYTHONPATH=os.pathsep.join([str(ref), str(ROOT), str(ROOT / "tests"), os.environ.get("PYTHONPATH", "")]))
     files = sorted(str(p) for p in (ref / "tests").glob("test_*.py"))
-    cmd = [sys.executable, "-m", "pytest", "-q", "-x", "--no-header", "-p", "ref_plugin", "-p", "no:cacheprovider",
+    cmd = [sys.executable, "-m", "pytest", "-q", "--no-header", "-p", "ref_plugin", "-p", "no:cacheprovider",
            "--rootdir", str(ref), "-c", os.devnull, *files]
     r = subprocess.run(cmd, env=env, cwd=str(ref), capture_output=True, text=True, timeout=2400)
     tail = (r.stdout + r.stderr)[-4000:]
@@ -200,6 +200,8 @@ def test_tsfast_own_test_files_pass_with_b200_installed(tmp_path):
     out_dir = ROOT / "gpurun_out"
     if out_dir.is_dir():
         (out_dir / "reference_tests_with_b200.json").write_text(json.dumps(rep, indent=1))
+    if out_dir.is_dir():
+        (out_dir / "reference_tests_with_b200.log").write_text((r.stdout + r.stderr)[-60000:])
     assert rep["failed"] == 0 and r.returncode == 0, (rep, tail)
     assert rep["passed"] > 100
     for slot in ("scan.diagonal", "scan.selective", "mamba.ssm", "mamba.conv", "dynonet.allpole"):

@@ -40,7 +40,7 @@ def _record(config, name, ours, theirs32, ref64):
     fo, ft = _outside(ours, ref64), _outside(theirs32, ref64)
     _TABLE.setdefault(config, {})[name] = {"b200_outside": fo, "ref_f32_outside": ft, "b200_maxnorm": rel_err(ours, ref64),
                                            "ref_f32_maxnorm": rel_err(theirs32, ref64)}
-    assert fo <= ft + SLACK, (config, name, fo, ft)
+    assert fo <= ft + max(SLACK, 1.0 / max(1, np.asarray(ref64).size)), (config, name, fo, ft)  # one element of slack on small tensors
     assert rel_err(ours, ref64) < REL, (config, name)
 
 
