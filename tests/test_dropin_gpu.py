@@ -84,14 +84,13 @@ def test_tsfast_models_on_b200_kernels_match_float64_reference(tsfast_installed,
     from tsfast.models import use_backend
 
     model32, counter = _build(m, family)
-    model64 = copy.deepcopy(model32).double()
     if family == "dynonet":  # dynoNet starts with a = 0; give the poles something to do
-        for mod in (model32, model64):
-            torch.manual_seed(1)
-            with torch.no_grad():
-                for p in mod.parameters():
-                    if p.dim() == 3 and p.shape[-1] == 2:
-                        p.normal_(0, 0.2)
+        torch.manual_seed(1)
+        with torch.no_grad():
+            for name, p in model32.named_parameters():
+                if name.endswith("a_coeff"):
+                    p.normal_(0, 0.2)
+    model64 = copy.deepcopy(model32).double()
     model32, model64 = model32.cuda(), model64.cuda()
     torch.manual_seed(2)
     u = torch.randn(4, 96, 3, device="cuda")
@@ -154,9 +153,17 @@ def test_compile_fullgraph_through_tsfast_modules(tsfast_installed, family):
 @pytest.mark.parametrize("family", ["lru", "mamba"])
 def test_graphed_stateful_model_of_tsfast(tsfast_installed, family):
     """tsfast's own CUDA-graph wrapper (flat state bridge, make_graphed_callables) around its own
-    model, running on these kernels: replay equals eager, forward and parameter gradients."""
+    model, running on these kernels: every replay equals eager, output and parameter gradients.
+
+    Gradients are compared step by step with ``.grad`` reset to None in between, as a training loop
+    does: a replayed backward returns its static gradient buffers, so accumulating over replays is
+    not something graphed callables support.  The Mamba model hands its (real) state from step to
+    step; for the LRU model every step starts from a zero state, because tsfast's flat-state bridge
+    stages the state in a float32 buffer and so drops the imaginary part of a complex state whatever
+    kernel computes it."""
     m = tsfast_installed
     from tsfast.models._core.cudagraph import GraphedStatefulModel
+    from tsfast.models._core.state import detach_state
 
     model, counter = _build(m, family)
     model = model.cuda()
@@ -167,19 +174,23 @@ def test_graphed_stateful_model_of_tsfast(tsfast_installed, family):
     state_g = state_e = None
     for step in range(3):
         u = torch.randn(4, 50, 3, device="cuda")
-        yg, state_g = graphed(u, state_g)
-        ye, state_e = eager(u, state=state_e)
+        for mod in (model, eager):
+            for p in mod.parameters():
+                p.grad = None
+        yg, new_g = graphed(u, state_g)
+        ye, new_e = eager(u, state=state_e)
         assert _rel(yg, ye) < 1e-5, step
         yg.square().mean().backward()
         ye.square().mean().backward()
-        from tsfast.models._core.state import detach_state
-
-        state_g, state_e = detach_state(state_g), detach_state(state_e)
+        for (name, p), q in zip(model.named_parameters(), eager.parameters()):
+            assert _rel(p.grad, q.grad) < 1e-4, (step, name)
+        if family == "mamba":
+            state_g, state_e = detach_state(new_g), detach_state(new_e)
+            for a, b in zip(torch.utils._pytree.tree_leaves(state_g), torch.utils._pytree.tree_leaves(state_e)):
+                assert _rel(a, b) < 1e-5, step
     assert not graphed._capture_failed, "tsfast fell back to eager: the capture failed"
     assert graphed._graphed is not None
     assert _launches()[counter] > before
-    for (name, p), q in zip(model.named_parameters(), eager.parameters()):
-        assert _rel(p.grad, q.grad) < 1e-4, name
 
 
 def test_tsfast_own_test_files_pass_with_b200_installed(tmp_path):
