@@ -207,6 +207,25 @@ int b200_conv_silu_bwd(int64_t B, int64_t L, int64_t D, int64_t K, const void* g
                        const void* bias, void* gx, void* gtail, void* gw, void* gb, void* workspace,
                        size_t workspace_bytes, void* stream);
 
+/* ---- Boundary projections of the LRU / S5 layers on the tensor cores ------------------------
+ * C[M,N] = A1[M,K1] * B1[N,K1]^T  (+ A2[M,K2] * B2[N,K2]^T when K2 > 0), float32 in and out.
+ * Replaces the two real GEMMs behind complex_in_proj / real_out_proj of
+ * tsfast/models/_core/scan.py:272-313 (called from architectures/lru.py:99,107 and s5.py:185,195) and
+ * the feed-through product added to the readout (lru.py:107): with the interleaved weight layouts
+ * those functions build, in-projection is (A1 = u, B1 = [2n, d]) and readout + feed-through is
+ * (A1 = view_as_real(x) [M, 2n], B1 = [out, 2n]; A2 = u, B2 = D).  The same entry point computes the
+ * input gradients (A1 = upstream gradient, B1 = the transposed weight).
+ * Arithmetic: tcgen05.mma.kind::tf32 with every operand split into a TF32 head and a float32 tail
+ * (three MMAs per product, float32 accumulation in tensor memory): float32-faithful, about 1e-6
+ * relative.  A1/A2 row-major with row pitches lda1/lda2 (floats, multiples of 4, 16-byte aligned
+ * base), B1/B2 row-major [N, K] with pitches ldb1/ldb2, C row-major with pitch ldc (multiple of 4,
+ * 16-byte aligned).  K1 and K2 must be multiples of 32 (B200_ERR_UNSUPPORTED otherwise); M and N are
+ * free.  The workspace holds the split weights and the status header (b200_workspace_status). */
+size_t b200_proj_gemm_workspace_bytes(int64_t N, int64_t K1, int64_t K2);
+int b200_proj_gemm(int64_t M, int64_t N, int64_t K1, const void* A1, int64_t lda1, const void* B1, int64_t ldb1,
+                   int64_t K2, const void* A2, int64_t lda2, const void* B2, int64_t ldb2, void* C, int64_t ldc,
+                   void* workspace, size_t workspace_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
