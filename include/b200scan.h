@@ -208,23 +208,37 @@ int b200_conv_silu_bwd(int64_t B, int64_t L, int64_t D, int64_t K, const void* g
                        size_t workspace_bytes, void* stream);
 
 /* ---- Boundary projections of the LRU / S5 layers on the tensor cores ------------------------
- * C[M,N] = A1[M,K1] * B1[N,K1]^T  (+ A2[M,K2] * B2[N,K2]^T when K2 > 0), float32 in and out.
+ * C[M,N] = A1[M,K1] * B1[N,K1]^T  (+ A2[M,K2] * B2[N,K2]^T when K2 > 0)  (+ bias[N] on every row when
+ * bias != NULL), float32 in and out.
  * Replaces the two real GEMMs behind complex_in_proj / real_out_proj of
  * tsfast/models/_core/scan.py:272-313 (called from architectures/lru.py:99,107 and s5.py:185,195) and
  * the feed-through product added to the readout (lru.py:107): with the interleaved weight layouts
  * those functions build, in-projection is (A1 = u, B1 = [2n, d]) and readout + feed-through is
- * (A1 = view_as_real(x) [M, 2n], B1 = [out, 2n]; A2 = u, B2 = D).  The same entry point computes the
- * input gradients (A1 = upstream gradient, B1 = the transposed weight).
- * Arithmetic: tcgen05.mma.kind::tf32 with every operand split into a TF32 head and a float32 tail
- * (three MMAs per product, float32 accumulation in tensor memory): float32-faithful, about 1e-6
+ * (A1 = view_as_real(x) [M, 2n], B1 = [out, 2n]; A2 = u, B2 = D).  With a bias it is also the
+ * x_proj / dt_proj pair that produces draw, B_t, C_t for the Mamba section
+ * (architectures/mamba/core.py:150-152).  The same entry point computes the input gradients
+ * (A1 = upstream gradient, B1 = the transposed weight).
+ * Arithmetic: tcgen05.mma.kind::tf32 with every operand split into a TF32 head and a TF32 tail
+ * (three MMAs per product, float32 accumulation in tensor memory): float32-faithful, a few 1e-6
  * relative.  A1/A2 row-major with row pitches lda1/lda2 (floats, multiples of 4, 16-byte aligned
  * base), B1/B2 row-major [N, K] with pitches ldb1/ldb2, C row-major with pitch ldc (multiple of 4,
- * 16-byte aligned).  K1 and K2 must be multiples of 32 (B200_ERR_UNSUPPORTED otherwise); M and N are
- * free.  The workspace holds the split weights and the status header (b200_workspace_status). */
+ * 16-byte aligned).  M, N, K1, K2 are free (partial tiles read zeros).  The workspace holds the split
+ * weights and the status header (b200_workspace_status). */
 size_t b200_proj_gemm_workspace_bytes(int64_t N, int64_t K1, int64_t K2);
 int b200_proj_gemm(int64_t M, int64_t N, int64_t K1, const void* A1, int64_t lda1, const void* B1, int64_t ldb1,
-                   int64_t K2, const void* A2, int64_t lda2, const void* B2, int64_t ldb2, void* C, int64_t ldc,
-                   void* workspace, size_t workspace_bytes, void* stream);
+                   int64_t K2, const void* A2, int64_t lda2, const void* B2, int64_t ldb2, const void* bias, void* C,
+                   int64_t ldc, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Weight gradient of such a product: dW[N,K] = G[M,N]^T * A[M,K], the reduction running over the M
+ * tokens.  Replaces what autograd runs for the weight of each of the GEMMs above (a float32 SIMT GEMM
+ * with a 256 000-long reduction in the full-model configuration).  Same arithmetic; both operands are
+ * read token-major in place (no transposed copy).  G and A row-major with pitches ldg / lda (multiples
+ * of 4, 16-byte aligned bases), dW row-major with pitch lddw.  The token axis is cut into slices that
+ * are accumulated in tensor memory and added in a fixed order, so results are reproducible; the
+ * workspace holds the slices' partial tiles. */
+size_t b200_proj_wgrad_workspace_bytes(int64_t M, int64_t N, int64_t K);
+int b200_proj_wgrad(int64_t M, int64_t N, int64_t K, const void* G, int64_t ldg, const void* A, int64_t lda, void* dW,
+                    int64_t lddw, void* workspace, size_t workspace_bytes, void* stream);
 
 #ifdef __cplusplus
 }

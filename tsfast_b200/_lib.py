@@ -50,7 +50,9 @@ SIGNATURES = {
     "b200_mamba_bwd_workspace_bytes": (_sz, [_i64] * 4),
     "b200_mamba_bwd": (_int, [_i64] * 4 + [_vp] * 20 + [_sz, _vp]),
     "b200_proj_gemm_workspace_bytes": (_sz, [_i64] * 3),
-    "b200_proj_gemm": (_int, [_i64, _i64, _i64, _vp, _i64, _vp, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _sz, _vp]),
+    "b200_proj_gemm": (_int, [_i64, _i64, _i64, _vp, _i64, _vp, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _i64, _vp, _sz, _vp]),
+    "b200_proj_wgrad_workspace_bytes": (_sz, [_i64] * 3),
+    "b200_proj_wgrad": (_int, [_i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _sz, _vp]),
     "b200_conv_silu_fwd": (_int, [_i64] * 4 + [_vp, _i64, _i64] + [_vp] * 5),
     "b200_conv_silu_bwd_workspace_bytes": (_sz, [_i64] * 4),
     "b200_conv_silu_bwd": (_int, [_i64] * 4 + [_vp, _vp, _i64, _i64] + [_vp] * 8 + [_sz, _vp]),

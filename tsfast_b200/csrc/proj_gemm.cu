@@ -4,9 +4,9 @@
 // (tens to hundreds), so each product is a skinny GEMM whose cost is reading A and writing C once;
 // the only reason it is slow as a float32 SIMT GEMM is arithmetic.  Here the arithmetic runs as
 // tcgen05.mma.kind::tf32 with float32-faithful numerics: every operand is split x = hi + lo with hi
-// the value truncated to TF32 (10 mantissa bits kept) and lo = x - hi (exact in float32), and the
-// product is accumulated in float32 in tensor memory as  hi*hi + hi*lo + lo*hi  (the dropped lo*lo
-// term is below 2^-22 relative).
+// the value rounded to TF32 (10 mantissa bits) and lo the rounded remainder, and the product is
+// accumulated in float32 in tensor memory as  lo*hi + hi*lo + hi*hi  (the dropped lo*lo term is below
+// 2^-22 relative).
 //
 // One CTA (128 threads) computes one 128 x 128 tile of C:
 //   * thread 0 asks the TMA unit for the next K-block (32 floats = one 128-byte swizzle row) of A and
@@ -37,6 +37,7 @@ constexpr int kWaitLimit = 200000;  // polls of an mbarrier (about 100 ns apart)
 
 struct ProjArgs {
     float* C;
+    const float* bias;  // [N] added to every row, or null
     long long ldc;
     long long M, N;
     int kb1, kb2;  // K-blocks of the first and of the second product
@@ -116,20 +117,27 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 
-// x = hi + lo with hi = x truncated to TF32 (sign, 8 exponent and 10 mantissa bits)
+// x = hi + lo (+ a remainder below 2^-22 |x|): hi is x rounded to the nearest TF32 value (10 mantissa bits)
+// and lo the rounded difference, so both halves are exactly what the tensor core will read and the
+// rounding errors carry no common sign
+__device__ __forceinline__ float round_tf32(float x) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return __uint_as_float(r);
+}
 __device__ __forceinline__ void split_tf32(float x, float& hi, float& lo) {
-    hi = __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);
-    lo = x - hi;
+    hi = round_tf32(x);
+    lo = round_tf32(x - hi);
 }
 
-// B[N, K] (row pitch ldb) -> hi[N, K], lo[N, K] dense
-__global__ void split_weights_kernel(const float* __restrict__ B, long long ldb, long long N, long long K,
+// B[N, K] (row pitch ldb) -> hi[N, Kp], lo[N, Kp] with Kp = K rounded up to 4 (16-byte row pitch for TMA)
+__global__ void split_weights_kernel(const float* __restrict__ B, long long ldb, long long N, long long K, long long Kp,
                                      float* __restrict__ hi, float* __restrict__ lo) {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= N * K) return;
-    const long long r = i / K, c = i - r * K;
-    float h, l;
-    split_tf32(B[r * ldb + c], h, l);
+    if (i >= N * Kp) return;
+    const long long r = i / Kp, c = i - r * Kp;
+    float h = 0.f, l = 0.f;
+    if (c < K) split_tf32(B[r * ldb + c], h, l);
     hi[i] = h;
     lo[i] = l;
 }
@@ -236,7 +244,13 @@ proj_gemm_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_constan
                 const long long grow = (long long)row0 + wid * 32 + r;
                 const long long gcol = (long long)col0 + c * 32 + cc;
                 if (grow < p.M && gcol < p.N) {
-                    const float4 o = *reinterpret_cast<const float4*>(patch + r * 36 + cc);
+                    float4 o = *reinterpret_cast<const float4*>(patch + r * 36 + cc);
+                    if (p.bias != nullptr) {
+                        o.x += p.bias[gcol];
+                        if (gcol + 1 < p.N) o.y += p.bias[gcol + 1];
+                        if (gcol + 2 < p.N) o.z += p.bias[gcol + 2];
+                        if (gcol + 3 < p.N) o.w += p.bias[gcol + 3];
+                    }
                     float* dst = p.C + grow * p.ldc + gcol;
                     if (gcol + 3 < p.N) {
                         __stcs(reinterpret_cast<float4*>(dst), o);
@@ -259,6 +273,178 @@ proj_gemm_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_constan
     }
 }
 
+
+// ================================================================================ weight gradient
+// dW[N, K] = G[M, N]^T * A[M, K]: the reduction runs over the tokens (rows of both operands), which are
+// the slow axis in memory, so both operands reach the tensor core "MN-major": a block of kTok tokens x
+// 32 columns lands as kTok rows of 128 bytes, swizzled in 32-byte chunks with a period of 4 rows (the
+// layout the tensor core expects of MN-major 4-byte elements), and the descriptor names the column
+// axis as the contiguous one (leading byte offset = distance between two 32-column blocks, stride
+// byte offset = 4 tokens = 512 bytes).  An MMA consumes 8 tokens; a CTA owns one
+// 128 x 128 tile of dW for one slice of the token axis, accumulates it in tensor memory over its whole
+// slice and writes it to the workspace; wgrad_reduce_kernel adds the slices in a fixed order.
+constexpr int kTok = 32;                         // tokens per block
+constexpr int kColBlk = kTok * 128;              // bytes of one 32-column block: kTok rows of 128 bytes
+constexpr uint32_t kIdescMN = kIdesc | (1u << 15) | (1u << 16);  // A and B MN-major
+
+__device__ __forceinline__ uint64_t umma_desc_mn_sw128(uint32_t saddr) {
+    uint64_t d = (uint64_t)((saddr >> 4) & 0x3FFFu);
+    d |= (uint64_t)(kColBlk >> 4) << 16;  // leading byte offset: next 32-column block
+    d |= (uint64_t)(512 >> 4) << 32;      // stride byte offset: next group of 4 tokens (the swizzle period)
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)1 << 61;               // 128-byte swizzle with a 32-byte base (4-byte elements, MN-major)
+    return d;
+}
+__device__ __forceinline__ void umma_tf32_mn(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "l"(adesc), "l"(bdesc), "r"(kIdescMN), "r"(accumulate)
+        : "memory");
+}
+
+struct WgradArgs {
+    float* part;        // [splits][N][Kp] partial sums
+    long long M, N, K, Kp;
+    long long tok_per_split;  // multiple of kTok
+    int n_tiles, k_tiles;
+    WsHeader* hdr;
+};
+
+__global__ void __launch_bounds__(128, 3)
+proj_wgrad_kernel(const __grid_constant__ CUtensorMap mapG, const __grid_constant__ CUtensorMap mapA, const WgradArgs p) {
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ __align__(8) uint64_t bar_tma, bar_mma;
+    __shared__ uint32_t tmem_base_slot;
+    const int tid = threadIdx.x, wid = tid >> 5, lane = tid & 31;
+    unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    float* sG = reinterpret_cast<float*>(base);                    // [4 column blocks][kTok][32]
+    float* sGlo = reinterpret_cast<float*>(base + kTileBytes);
+    float* sA = reinterpret_cast<float*>(base + 2 * kTileBytes);
+    float* sAlo = reinterpret_cast<float*>(base + 3 * kTileBytes);
+
+    const int tiles = p.n_tiles * p.k_tiles;
+    const int split = blockIdx.x / tiles, t = blockIdx.x - split * tiles;
+    const int n_tile = t / p.k_tiles, k_tile = t - n_tile * p.k_tiles;
+    const int n0 = n_tile * 128, k0 = k_tile * 128;
+    const long long tok0 = (long long)split * p.tok_per_split;
+    long long tok1 = tok0 + p.tok_per_split;
+    if (tok1 > p.M) tok1 = p.M;
+    const int nblk = tok1 > tok0 ? (int)((tok1 - tok0 + kTok - 1) / kTok) : 0;
+
+    if (tid == 0) {
+        mbar_init(&bar_tma, 1);
+        mbar_init(&bar_mma, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (wid == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(128)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_d = tmem_base_slot;
+
+    int ok = 1;
+    for (int kb = 0; kb < nblk && ok; ++kb) {
+        const uint32_t parity = (uint32_t)(kb & 1);
+        if (tid == 0) {
+            // rows past the slice's end but inside M belong to the next slice: the tensor maps cannot mask
+            // them, so slices are whole multiples of kTok and only the last one meets the end of the matrix
+            const int row = (int)(tok0 + (long long)kb * kTok);
+            mbar_expect_tx(&bar_tma, 2 * kTileBytes);
+#pragma unroll
+            for (int cb = 0; cb < 4; ++cb) {
+                tma_load_2d(reinterpret_cast<unsigned char*>(sG) + cb * kColBlk, &mapG, n0 + cb * 32, row, &bar_tma);
+                tma_load_2d(reinterpret_cast<unsigned char*>(sA) + cb * kColBlk, &mapA, k0 + cb * 32, row, &bar_tma);
+            }
+        }
+        const int landed = mbar_wait(&bar_tma, parity) ? 1 : 0;
+#pragma unroll
+        for (int j = 0; j < kTileBytes / 16 / 128; ++j) {
+            float4 x = reinterpret_cast<float4*>(sG)[j * 128 + tid], y = reinterpret_cast<float4*>(sA)[j * 128 + tid];
+            float4 h, l;
+            split_tf32(x.x, h.x, l.x), split_tf32(x.y, h.y, l.y), split_tf32(x.z, h.z, l.z), split_tf32(x.w, h.w, l.w);
+            reinterpret_cast<float4*>(sG)[j * 128 + tid] = h;
+            reinterpret_cast<float4*>(sGlo)[j * 128 + tid] = l;
+            split_tf32(y.x, h.x, l.x), split_tf32(y.y, h.y, l.y), split_tf32(y.z, h.z, l.z), split_tf32(y.w, h.w, l.w);
+            reinterpret_cast<float4*>(sA)[j * 128 + tid] = h;
+            reinterpret_cast<float4*>(sAlo)[j * 128 + tid] = l;
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        ok = __syncthreads_and(landed);
+        if (ok) {
+            if (tid == 0) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint64_t dG = umma_desc_mn_sw128(smem_u32(sG)), dGl = umma_desc_mn_sw128(smem_u32(sGlo));
+                const uint64_t dA = umma_desc_mn_sw128(smem_u32(sA)), dAl = umma_desc_mn_sw128(smem_u32(sAlo));
+#pragma unroll
+                for (int g = 0; g < kTok / 8; ++g) {  // 8 tokens per MMA: the next 1024-byte group
+                    const uint64_t adv = (uint64_t)(g * (1024 >> 4));
+                    umma_tf32_mn(tmem_d, dGl + adv, dA + adv, (kb | g) != 0);
+                    umma_tf32_mn(tmem_d, dG + adv, dAl + adv, 1u);
+                    umma_tf32_mn(tmem_d, dG + adv, dA + adv, 1u);
+                }
+                umma_commit(&bar_mma);
+            }
+            ok = __syncthreads_and(mbar_wait(&bar_mma, parity) ? 1 : 0);
+        }
+    }
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+
+    if (ok) {
+        // accumulator lane = row of dW (column of G), accumulator column = column of dW (column of A)
+        float* patch = reinterpret_cast<float*>(base) + wid * (32 * 36);
+        float* dst_tile = p.part + (long long)split * p.N * p.Kp;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+            float v[32];
+            if (nblk > 0) {
+                tmem_ld32(tmem_d + ((uint32_t)(wid * 32) << 16) + (uint32_t)(c * 32), v);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] = 0.f;
+            }
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+                *reinterpret_cast<float4*>(patch + lane * 36 + q * 4) = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+            __syncwarp();
+            const int cc = (lane & 7) * 4;
+#pragma unroll
+            for (int rr = 0; rr < 8; ++rr) {
+                const int r = rr * 4 + (lane >> 3);
+                const long long grow = (long long)n0 + wid * 32 + r, gcol = (long long)k0 + c * 32 + cc;
+                if (grow < p.N && gcol < p.Kp)  // Kp is a multiple of 4: whole float4 pieces
+                    *reinterpret_cast<float4*>(dst_tile + grow * p.Kp + gcol) = *reinterpret_cast<const float4*>(patch + r * 36 + cc);
+            }
+            __syncwarp();
+        }
+    } else if (tid == 0) {
+        atomicExch(&p.hdr->error, (unsigned int)B200_ERR_TIMEOUT);
+        for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (wid == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(128) : "memory");
+    }
+}
+
+// dW[n][k] = sum over slices of part[s][n][k], slices in ascending order (fixed, so reproducible)
+__global__ void wgrad_reduce_kernel(const float* __restrict__ part, int splits, long long N, long long K, long long Kp,
+                                    float* __restrict__ dW, long long lddw) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= N * K) return;
+    const long long n = i / K, k = i - n * K;
+    float s = 0.f;
+    for (int sp = 0; sp < splits; ++sp) s += part[((long long)sp * N + n) * Kp + k];
+    dW[n * lddw + k] = s;
+}
+
 // ------------------------------------------------------------------------------- host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -277,31 +463,57 @@ static EncodeTiledFn encode_fn() {
 }
 
 // Tensor map of a row-major float32 matrix [rows, cols] (row pitch ld floats) read in boxes of
-// kBK columns x 128 rows into the 128-byte-swizzled layout; rows and columns past the end read as zero.
-static bool make_map(CUtensorMap* map, const float* ptr, long long rows, long long cols, long long ld) {
+// kBK columns x box_rows rows into the 128-byte-swizzled layout; rows and columns past the end read as zero.
+static bool make_map(CUtensorMap* map, const float* ptr, long long rows, long long cols, long long ld, int box_rows = kBM,
+                     CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
     EncodeTiledFn fn = encode_fn();
     if (fn == nullptr) return false;
     const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
     const cuuint64_t strides[1] = {(cuuint64_t)ld * sizeof(float)};
-    const cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)kBM};
+    const cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)box_rows};
     const cuuint32_t estr[2] = {1, 1};
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(ptr), dims, strides, box, estr,
-              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 struct ProjWs {
     size_t off_b1hi, off_b1lo, off_b2hi, off_b2lo, total;
 };
+static long long pad4(long long k) { return (k + 3) / 4 * 4; }
 static ProjWs proj_ws(long long N, long long K1, long long K2) {
     ProjWs w;
     size_t off = align_up(sizeof(WsHeader), 256);
-    const size_t s1 = align_up(sizeof(float) * (size_t)(N * K1), 256), s2 = align_up(sizeof(float) * (size_t)(N * K2), 256);
+    const size_t s1 = align_up(sizeof(float) * (size_t)(N * pad4(K1)), 256), s2 = align_up(sizeof(float) * (size_t)(N * pad4(K2)), 256);
     w.off_b1hi = off, off += s1;
     w.off_b1lo = off, off += s1;
     w.off_b2hi = off, off += s2;
     w.off_b2lo = off, off += s2;
     w.total = off;
+    return w;
+}
+
+
+// Token slices of the weight gradient: enough CTAs for about three per SM, slices a multiple of kTok.
+struct WgradPlan {
+    int n_tiles, k_tiles, splits;
+    long long tok_per_split, Kp;
+    size_t off_part, total;
+};
+static WgradPlan wgrad_plan(long long M, long long N, long long K) {
+    WgradPlan w;
+    w.n_tiles = (int)((N + 127) / 128), w.k_tiles = (int)((K + 127) / 128);
+    w.Kp = pad4(K);
+    const long long tiles = (long long)w.n_tiles * w.k_tiles;
+    long long want = (3 * 148 + tiles - 1) / tiles;  // slices so that every SM has about three CTAs
+    const long long blocks = (M + kTok - 1) / kTok;
+    if (want > blocks) want = blocks;
+    if (want < 1) want = 1;
+    const long long bps = (blocks + want - 1) / want;  // token blocks per slice
+    w.tok_per_split = bps * kTok;
+    w.splits = (int)((blocks + bps - 1) / bps);
+    w.off_part = align_up(sizeof(WsHeader), 256);
+    w.total = w.off_part + align_up(sizeof(float) * (size_t)w.splits * (size_t)N * (size_t)w.Kp, 256);
     return w;
 }
 
@@ -317,12 +529,11 @@ size_t b200_proj_gemm_workspace_bytes(int64_t N, int64_t K1, int64_t K2) {
 }
 
 int b200_proj_gemm(int64_t M, int64_t N, int64_t K1, const void* A1, int64_t lda1, const void* B1, int64_t ldb1,
-                   int64_t K2, const void* A2, int64_t lda2, const void* B2, int64_t ldb2, void* C, int64_t ldc,
-                   void* workspace, size_t workspace_bytes, void* stream) {
+                   int64_t K2, const void* A2, int64_t lda2, const void* B2, int64_t ldb2, const void* bias, void* C,
+                   int64_t ldc, void* workspace, size_t workspace_bytes, void* stream) {
     using namespace b200;
     if (M < 0 || N <= 0 || K1 <= 0 || K2 < 0) return B200_ERR_ARG;
     if (M == 0) return B200_OK;
-    if (K1 % kBK != 0 || K2 % kBK != 0) return B200_ERR_UNSUPPORTED;
     if (!row_ok(A1, lda1) || !B1 || !C || ldc < N || lda1 < K1 || ldb1 < K1) return B200_ERR_ARG;
     if (K2 > 0 && (!row_ok(A2, lda2) || !B2 || lda2 < K2 || ldb2 < K2)) return B200_ERR_ARG;
     if (((uintptr_t)C & 15) != 0 || ldc % 4 != 0) return B200_ERR_ARG;
@@ -337,15 +548,16 @@ int b200_proj_gemm(int64_t M, int64_t N, int64_t K1, const void* A1, int64_t lda
     float* b1lo = (float*)(base + w.off_b1lo);
     float* b2hi = (float*)(base + w.off_b2hi);
     float* b2lo = (float*)(base + w.off_b2lo);
-    split_weights_kernel<<<(unsigned int)((N * K1 + 255) / 256), 256, 0, st>>>((const float*)B1, ldb1, N, K1, b1hi, b1lo);
+    const long long K1p = pad4(K1), K2p = pad4(K2);
+    split_weights_kernel<<<(unsigned int)((N * K1p + 255) / 256), 256, 0, st>>>((const float*)B1, ldb1, N, K1, K1p, b1hi, b1lo);
     if (K2 > 0)
-        split_weights_kernel<<<(unsigned int)((N * K2 + 255) / 256), 256, 0, st>>>((const float*)B2, ldb2, N, K2, b2hi, b2lo);
+        split_weights_kernel<<<(unsigned int)((N * K2p + 255) / 256), 256, 0, st>>>((const float*)B2, ldb2, N, K2, K2p, b2hi, b2lo);
     if (cudaGetLastError() != cudaSuccess) return B200_ERR_LAUNCH;
 
     CUtensorMap mA1, mB1h, mB1l, mA2, mB2h, mB2l;
-    bool ok = make_map(&mA1, (const float*)A1, M, K1, lda1) && make_map(&mB1h, b1hi, N, K1, K1) && make_map(&mB1l, b1lo, N, K1, K1);
+    bool ok = make_map(&mA1, (const float*)A1, M, K1, lda1) && make_map(&mB1h, b1hi, N, K1, K1p) && make_map(&mB1l, b1lo, N, K1, K1p);
     if (K2 > 0) {
-        ok = ok && make_map(&mA2, (const float*)A2, M, K2, lda2) && make_map(&mB2h, b2hi, N, K2, K2) && make_map(&mB2l, b2lo, N, K2, K2);
+        ok = ok && make_map(&mA2, (const float*)A2, M, K2, lda2) && make_map(&mB2h, b2hi, N, K2, K2p) && make_map(&mB2l, b2lo, N, K2, K2p);
     } else {
         mA2 = mA1, mB2h = mB1h, mB2l = mB1l;
     }
@@ -360,10 +572,55 @@ int b200_proj_gemm(int64_t M, int64_t N, int64_t K1, const void* A1, int64_t lda
         configured[dev] = true;
     }
     ProjArgs a;
-    a.C = (float*)C, a.ldc = ldc, a.M = M, a.N = N;
-    a.kb1 = (int)(K1 / kBK), a.kb2 = (int)(K2 / kBK);
+    a.C = (float*)C, a.bias = (const float*)bias, a.ldc = ldc, a.M = M, a.N = N;
+    a.kb1 = (int)((K1 + kBK - 1) / kBK), a.kb2 = (int)((K2 + kBK - 1) / kBK);  // a ragged last block reads zeros past K
     a.hdr = reinterpret_cast<WsHeader*>(base);
     proj_gemm_kernel<<<(unsigned int)tiles, 128, kGemmSmem, st>>>(mA1, mB1h, mB1l, mA2, mB2h, mB2l, a);
+    return cudaGetLastError() == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
+}
+
+size_t b200_proj_wgrad_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+    if (M <= 0 || N <= 0 || K <= 0) return 256;
+    return b200::wgrad_plan(M, N, K).total;
+}
+
+int b200_proj_wgrad(int64_t M, int64_t N, int64_t K, const void* G, int64_t ldg, const void* A, int64_t lda, void* dW,
+                    int64_t lddw, void* workspace, size_t workspace_bytes, void* stream) {
+    using namespace b200;
+    if (M < 0 || N <= 0 || K <= 0 || !dW || lddw < K) return B200_ERR_ARG;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (M == 0) {
+        if (cudaMemset2DAsync(dW, (size_t)lddw * 4, 0, (size_t)K * 4, (size_t)N, st) != cudaSuccess) return B200_ERR_LAUNCH;
+        return B200_OK;
+    }
+    if (!row_ok(G, ldg) || !row_ok(A, lda) || ldg < N || lda < K) return B200_ERR_ARG;
+    const WgradPlan w = wgrad_plan(M, N, K);
+    if (!workspace || ((uintptr_t)workspace % 256) != 0 || workspace_bytes < w.total) return B200_ERR_WORKSPACE;
+    char* base = static_cast<char*>(workspace);
+    if (cudaMemsetAsync(base, 0, sizeof(WsHeader), st) != cudaSuccess) return B200_ERR_LAUNCH;
+    CUtensorMap mG, mA;
+    // token-major operands of 4-byte elements use the 128-byte swizzle whose unit is a 32-byte chunk
+    if (!make_map(&mG, (const float*)G, M, N, ldg, kTok, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B) ||
+        !make_map(&mA, (const float*)A, M, K, lda, kTok, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B))
+        return B200_ERR_LAUNCH;
+    static bool configured[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        if (cudaFuncSetAttribute(proj_wgrad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem) != cudaSuccess)
+            return B200_ERR_LAUNCH;
+        configured[dev] = true;
+    }
+    WgradArgs a;
+    a.part = (float*)(base + w.off_part);
+    a.M = M, a.N = N, a.K = K, a.Kp = w.Kp, a.tok_per_split = w.tok_per_split;
+    a.n_tiles = w.n_tiles, a.k_tiles = w.k_tiles;
+    a.hdr = reinterpret_cast<WsHeader*>(base);
+    const long long grid = (long long)w.splits * w.n_tiles * w.k_tiles;
+    if (grid > 0x7fffffffLL) return B200_ERR_UNSUPPORTED;
+    proj_wgrad_kernel<<<(unsigned int)grid, 128, kGemmSmem, st>>>(mG, mA, a);
+    if (cudaGetLastError() != cudaSuccess) return B200_ERR_LAUNCH;
+    wgrad_reduce_kernel<<<(unsigned int)((N * K + 255) / 256), 256, 0, st>>>(a.part, w.splits, N, K, w.Kp, (float*)dW, lddw);
     return cudaGetLastError() == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
 }
 
