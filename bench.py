@@ -345,6 +345,9 @@ def run_gpu(args):
             torch.cuda.empty_cache()
         try:
             c5 = _c5_measure(torch, dist, dev, world, rank, local, barrier, steps=max(5, min(args.steps, 10)), warmup=3)
+            if world == 1:  # the same step with the GEMMs left to PyTorch: what the tensor-core projections buy
+                c5["ms_per_step_gemms_in_pytorch"] = _c5_measure(torch, dist, dev, world, rank, local, barrier, steps=5,
+                                                                 warmup=3, plain_gemms=True)["ms_per_step"]
         except ImportError as e:  # no tsfast copy on this machine: the step's caller is missing, not the kernels
             c5 = None
             others["C5"] = {"unavailable": f"{e}"[:200]}
@@ -862,7 +865,7 @@ def run_workload(args):
 C5_SHAPE = dict(windows=128, T=2000, d_model=128, d_state=256, n_layers=4)
 
 
-def _c5_setup(torch, dev, rank):
+def _c5_setup(torch, dev, rank, plain_gemms=False):
     """C5: DeepLRU (1 in, 1 out, 4 blocks, width 128, 256 complex states), 128 windows of T=2000 per
     GPU: band-limited Gaussian noise in (sigma 0.1, cut-off 0.4 Nyquist), a seeded stable 2nd-order
     filter followed by tanh as target.  Replicas start identical (same seed on every rank)."""
@@ -876,7 +879,8 @@ def _c5_setup(torch, dev, rank):
     _import_reference()
     from tsfast.models import DeepLRU
 
-    tsfast_b200.install()
+    tsfast_b200.uninstall()
+    tsfast_b200.install(fuse_projections=not plain_gemms)
     Bn, T_, dm, ds, nl = (C5_SHAPE[k] for k in ("windows", "T", "d_model", "d_state", "n_layers"))
     rng = np.random.default_rng(100 + rank)
     bl, al = signal.butter(4, 0.4)
@@ -890,6 +894,8 @@ def _c5_setup(torch, dev, rank):
     hy = torch.from_numpy(y_np.astype(np.float32)).unsqueeze(-1).pin_memory()
     torch.manual_seed(0)
     model = DeepLRU(1, 1, d_model=dm, d_state=ds, n_layers=nl, r_min=0.0, r_max=1.0).to(dev)
+    if not plain_gemms:  # boundary projections (install above) and every nn.Linear on the tcgen05 GEMM
+        tsfast_b200.accelerate_linears(model)
     opt = torch.optim.Adam(model.parameters(), lr=1e-3)
     return model, opt, hx, hy
 
@@ -912,10 +918,11 @@ def _c5_step_fn(torch, model, opt, ar_events):
     return step
 
 
-def _c5_measure(torch, dist, dev, world, rank, local, barrier, steps, warmup):
+def _c5_measure(torch, dist, dev, world, rank, local, barrier, steps, warmup, plain_gemms=False):
     """`steps` DeepLRU training steps (forward, MSE, backward, one flat-bucket NCCL all-reduce of the
-    gradients, Adam) between two events; this rank's time (the caller takes the max over ranks)."""
-    model, opt, hx, hy = _c5_setup(torch, dev, rank)
+    gradients, Adam) between two events; this rank's time (the caller takes the max over ranks).
+    `plain_gemms` leaves the model's GEMMs to PyTorch (float32 cuBLAS) for comparison."""
+    model, opt, hx, hy = _c5_setup(torch, dev, rank, plain_gemms)
     xb, yb = hx.to(dev), hy.to(dev)
     ar = []
     step = _c5_step_fn(torch, model, opt, ar)

@@ -118,6 +118,53 @@ def test_tsfast_models_on_b200_kernels_match_float64_reference(tsfast_installed,
     assert _rel(again, got) < 1e-6
 
 
+@pytest.mark.parametrize("family", ["lru", "s5", "mamba"])
+def test_projections_on_tensor_cores_match_float64_reference(tsfast_installed, family):
+    """install(fuse_projections=True) + accelerate_linears(model): tsfast's own model with every GEMM of the
+    step (boundary projections, encoder/decoder, GLU, Mamba's in/x/dt/out projections) on the tcgen05
+    kernel, against the float64 reference path: output and every parameter gradient."""
+    m = tsfast_installed
+    import tsfast_b200
+    from tsfast.models import use_backend
+    from tsfast_b200 import proj_b200
+
+    torch.manual_seed(0)
+    if family == "lru":
+        model32 = m.DeepLRU(3, 2, d_model=64, d_state=96, n_layers=2, return_state=True)
+    elif family == "s5":
+        model32 = m.DeepS5(3, 2, d_model=64, d_state=64, n_layers=2, return_state=True)
+    else:
+        model32 = m.DeepMamba(3, 2, d_model=64, d_state=16, n_layers=2, return_state=True)
+    model64 = copy.deepcopy(model32).double().cuda()
+    model32 = model32.cuda()
+    u = torch.randn(4, 200, 3, device="cuda")
+    tsfast_b200.install(fuse_projections=True)
+    n_lin = tsfast_b200.accelerate_linears(model32)
+    assert n_lin >= 2
+    before = proj_b200.calls
+    try:
+        with use_backend("auto"):
+            got = _chunked(model32, u, (90,))
+            (got**2).mean().backward()
+        used = proj_b200.calls - before
+        assert used >= 6 * n_lin // 2, f"only {used} launches of the projection kernels"
+        with use_backend("reference"):
+            want = _chunked(model64, u.double(), (90,))
+            (want**2).mean().backward()
+        assert _rel(got, want) < MODEL_TOL
+        for (name, p), q in zip(model32.named_parameters(), model64.parameters()):
+            assert p.grad is not None, name
+            assert _rel(p.grad, q.grad) < MODEL_TOL, name
+    finally:
+        assert tsfast_b200.restore_linears(model32) == n_lin
+        tsfast_b200.uninstall()
+        tsfast_b200.install()  # the module fixture keeps the scan backends installed
+    with use_backend("auto"), torch.no_grad():
+        before = proj_b200.calls
+        model32(u)
+        assert proj_b200.calls == before, "the projections were not restored"
+
+
 def test_reference_preference_bypasses_b200(tsfast_installed):
     m = tsfast_installed
     from tsfast.models import use_backend

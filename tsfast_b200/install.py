@@ -7,6 +7,15 @@ module object.  ``"triton"`` is the family tsfast tries first on CUDA under ``"a
 ``uninstall()`` restores what was there.  tsfast's source is not modified and tsfast need not be
 present for the rest of this package to work.
 
+The boundary projections of the LRU and S5 layers (``complex_in_proj`` / ``real_out_proj``,
+``_core/scan.py:272-313``) and the ``nn.Linear`` layers around the scans have no registry either.
+``install(fuse_projections=True)`` rebinds the two functions in tsfast's ``lru`` and ``s5`` modules to
+wrappers that run ``proj_b200``'s tensor-core GEMM when it supports the operands (float32 CUDA, backend
+preference "auto" or "triton") and tsfast's own function otherwise; ``accelerate_linears(model)`` does
+the same for every ``nn.Linear`` inside one model (encoder, decoder, GLU, Mamba's in/x/dt/out
+projections) by giving each instance a forward that calls ``proj_b200.linear``; ``restore_linears``
+undoes it.  Parameters and state dicts are untouched.
+
 dynoNet's linear block has no registry of its own (only its all-pole step has), so the fused block
 of ``dynonet_b200`` is offered as an opt-in: ``install(fuse_dynonet=True)`` wraps
 ``LinearDynamicalOperator.forward`` (``dynonet/core.py:199-254``) so that calls the fused kernels
@@ -18,6 +27,8 @@ method; ``uninstall()`` puts the original method back.
 from __future__ import annotations
 
 import importlib
+
+import torch
 
 _saved: dict[tuple[str, str], object] = {}
 _KEY = "triton"
@@ -63,11 +74,94 @@ def _wrap_dynonet_forward():
     cls.forward = forward
 
 
-def install(fuse_dynonet: bool = False) -> list[str]:
+_PROJ_USERS = ("tsfast.models.architectures.lru", "tsfast.models.architectures.s5")
+
+
+def _preference() -> str:
+    dispatch = importlib.import_module("tsfast.models._core.dispatch")
+    return dispatch.get_backend()
+
+
+def _wrap_projections():
+    from . import proj_b200
+
+    scan = importlib.import_module("tsfast.models._core.scan")
+    if ("proj", "complex_in_proj") in _saved:
+        return
+    orig_in, orig_out = scan.complex_in_proj, scan.real_out_proj
+
+    def complex_in_proj(u, W_re, W_im):
+        if _preference() in ("auto", _KEY) and proj_b200.supports(u, W_re) is None and W_im.dtype == W_re.dtype:
+            return proj_b200.complex_in_proj(u, W_re, W_im)
+        return orig_in(u, W_re, W_im)
+
+    def real_out_proj(x, W_re, W_im):
+        if (_preference() in ("auto", _KEY) and x.is_complex() and x.dtype == torch.complex64 and x.device.type == "cuda"
+                and W_re.dtype == torch.float32 and W_re.device.type == "cuda"):
+            return proj_b200.real_out_proj(x, W_re, W_im)
+        return orig_out(x, W_re, W_im)
+
+    complex_in_proj.__doc__, real_out_proj.__doc__ = orig_in.__doc__, orig_out.__doc__
+    _saved[("proj", "complex_in_proj")] = orig_in
+    _saved[("proj", "real_out_proj")] = orig_out
+    for name in _PROJ_USERS:  # the layers imported the two names into their own namespaces
+        mod = importlib.import_module(name)
+        mod.complex_in_proj, mod.real_out_proj = complex_in_proj, real_out_proj
+
+
+def _unwrap_projections():
+    orig_in = _saved.pop(("proj", "complex_in_proj"), None)
+    orig_out = _saved.pop(("proj", "real_out_proj"), None)
+    if orig_in is None:
+        return
+    for name in _PROJ_USERS:
+        mod = importlib.import_module(name)
+        mod.complex_in_proj, mod.real_out_proj = orig_in, orig_out
+
+
+def accelerate_linears(model) -> int:
+    """Give every ``nn.Linear`` inside ``model`` a forward on the tensor-core GEMM; returns how many.
+
+    The replacement calls ``proj_b200.linear(x, weight, bias)`` whenever that kernel supports the
+    operands and ``F.linear`` otherwise (CPU tensors, other dtypes), so the module keeps working
+    everywhere.  Weights, biases and state dicts are not touched; ``restore_linears(model)`` removes the
+    per-instance forwards again."""
+    import torch.nn.functional as F
+    from torch import nn
+
+    from . import proj_b200
+
+    def fast_forward(self, x):
+        if x.is_cuda and x.dtype == torch.float32 and proj_b200.supports(x, self.weight) is None:
+            return proj_b200.linear(x, self.weight, self.bias)
+        return F.linear(x, self.weight, self.bias)
+
+    count = 0
+    for mod in model.modules():
+        if type(mod) is nn.Linear and "forward" not in mod.__dict__:
+            mod.forward = fast_forward.__get__(mod, nn.Linear)
+            count += 1
+    return count
+
+
+def restore_linears(model) -> int:
+    """Remove the per-instance forwards ``accelerate_linears`` installed; returns how many."""
+    from torch import nn
+
+    count = 0
+    for mod in model.modules():
+        if type(mod) is nn.Linear and "forward" in mod.__dict__:
+            del mod.__dict__["forward"]
+            count += 1
+    return count
+
+
+def install(fuse_dynonet: bool = False, fuse_projections: bool = False) -> list[str]:
     """Route tsfast's CUDA scan dispatch to the B200 kernels; returns the slots replaced.
 
     With ``fuse_dynonet`` the whole dynoNet linear block (numerator, denominator, pair sum) also
-    runs as one fused kernel where its shapes allow (see the module docstring)."""
+    runs as one fused kernel where its shapes allow; with ``fuse_projections`` the LRU / S5 boundary
+    projections run on the tensor-core GEMM (see the module docstring)."""
     done = []
     for registry, slot, mod in _targets():
         if (slot, _KEY) not in _saved:
@@ -77,6 +171,9 @@ def install(fuse_dynonet: bool = False) -> list[str]:
     if fuse_dynonet:
         _wrap_dynonet_forward()
         done.append("dynonet.block")
+    if fuse_projections:
+        _wrap_projections()
+        done.append("scan.projections")
     return done
 
 
@@ -84,6 +181,7 @@ def uninstall() -> None:
     """Restore tsfast's own backends."""
     if not _saved:
         return
+    _unwrap_projections()
     original = _saved.pop(("dynonet.block", "forward"), None)
     if original is not None:
         importlib.import_module("tsfast.models.architectures.dynonet.core").LinearDynamicalOperator.forward = original
