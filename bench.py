@@ -6,7 +6,7 @@ h0 = 0, upstream gradient ~ N(0,1), all synthetic and seeded.  One step = one fo
 of compulsory HBM traffic, the figure every GB/s number below is computed from.  With N GPUs every
 rank scans its own 64 sequences (weak scaling; the scan has no collective).
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload C1..C5|G|V]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload C1..C5|G|V|P]
 
 Prints ONE JSON line: `value` is device-resident throughput (inputs already in HBM), `e2e` the
 same metric through the public API from pinned HOST buffers with the host<->device copies inside
@@ -19,8 +19,8 @@ The default run also measures, kernel-only and with the same event method, the o
 (`config.workloads`: C1 complex LRU scan, C3 Mamba section, C4 all-pole filter), the DeepLRU
 data-parallel training step (`config.c5`) and, on one GPU, the reference's own Triton kernels on
 the same device (`config.triton`, `config.vs_triton`).
-`--workload C1|C3|C4|C5|G|V` prints a full line for one of the other configurations (G the fused
-dynoNet block, V the Mamba causal conv + SiLU); C2 is the headline.
+`--workload C1|C3|C4|C5|G|V|P` prints a full line for one of the other configurations (G the fused
+dynoNet block, V the Mamba causal conv + SiLU, P the tensor-core projection GEMM); C2 is the headline.
 
 A rank that fails prints one `{"rank", "error", "where"}` JSON line to stdout and stderr before it
 exits non-zero.
@@ -719,6 +719,52 @@ def _workload(name, torch, dev, rank, host_buffers=True, impl="b200"):
                     traffic=286_489_088 + 96_544_000,  # ncu dram__bytes read + write of one adjoint launch at this shape
                     fwd=lambda: conv_b200._conv_silu_op(x, tail, w, bias),
                     bwd=lambda o: conv_b200._conv_silu_bwd_op(gy, x, tail, w, bias), e2e=e2e, cpu=cpu)
+    if name == "P":
+        from tsfast_b200 import proj_b200
+
+        # the in-projection of one DeepLRU layer of C5: 128 windows x 2000 steps, 128 features -> 256 complex states
+        Mt, K_, N_ = 256000, 128, 512
+        a_ = rn(Mt, K_)
+        w_ = rn(N_, K_) / K_**0.5
+        g_ = rn(Mt, N_)
+        big, small = Mt * N_ * 4, Mt * K_ * 4
+        ha, hg, hy, hga = pin(a_), pin(g_), pin(g_), pin(a_)
+
+        def e2e():
+            da = ha.to(dev, non_blocking=True).requires_grad_()
+            ww = w_.clone().requires_grad_()
+            y = proj_b200.linear(da, ww)
+            y.backward(hg.to(dev, non_blocking=True))
+            hy.copy_(y.detach(), non_blocking=True)
+            hga.copy_(da.grad, non_blocking=True)
+            return ww.grad.cpu()
+
+        def cpu(rows):
+            import numpy as np_
+
+            an, wn, gn = a_[: rows * 2000].cpu().numpy(), w_.cpu().numpy(), g_[: rows * 2000].cpu().numpy()
+            return lambda: (an @ wn.T, gn @ wn, gn.T @ an)
+
+        def extra(timed):
+            wt = w_.t().contiguous()
+            prev = torch.backends.cuda.matmul.allow_tf32
+            torch.backends.cuda.matmul.allow_tf32 = False
+            a_ @ wt  # the first call of each mode picks its cuBLAS algorithm
+            f32 = timed(lambda: a_ @ wt, 5)
+            torch.backends.cuda.matmul.allow_tf32 = True
+            a_ @ wt
+            tf32 = timed(lambda: a_ @ wt, 5)
+            torch.backends.cuda.matmul.allow_tf32 = prev
+            return {"forward_pytorch_float32_ms": round(f32, 4), "forward_pytorch_tf32_ms": round(tf32, 4),
+                    "flops_per_step": 3 * 2 * Mt * K_ * N_, "arithmetic": "tcgen05.mma.kind::tf32, 3 MMAs per product (hi/lo split)"}
+
+        return dict(desc="P: LRU in-projection GEMM of C5, 256000 tokens x 128 features -> 512 (256 complex states) fp32, "
+                         "forward + input gradient + weight gradient",
+                    fwd_bytes=big + small, bwd_bytes=2 * (big + small), elems=Mt * N_, rows=128, sample_rows=8, flush=False,
+                    h2d=big + small, d2h=big + small, dtype="f32 (tf32 x3)", launches=6,
+                    kernel="proj_gemm_kernel + proj_wgrad_kernel (b200_proj_gemm, b200_proj_wgrad)",
+                    fwd=lambda: proj_b200._proj_gemm_op(a_, w_, None),
+                    bwd=lambda o: (proj_b200._input_grad(g_, w_), proj_b200._proj_wgrad_op(g_, a_)), e2e=e2e, cpu=cpu, extra=extra)
     if name == "G":
         from tsfast_b200 import dynonet_b200
 
@@ -1054,7 +1100,7 @@ def main():
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
-    ap.add_argument("--workload", choices=["C1", "C2", "C3", "C4", "C5", "G", "V"], default="C2")
+    ap.add_argument("--workload", choices=["C1", "C2", "C3", "C4", "C5", "G", "V", "P"], default="C2")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
     ap.add_argument("--no-triton", action="store_true", help="skip the reference's Triton kernels (single-GPU baseline leg)")
     ap.add_argument("--kernel-only", action="store_true",

@@ -97,6 +97,26 @@ __device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint6
         "l"(adesc), "l"(bdesc), "r"(kIdesc), "r"(accumulate)
         : "memory");
 }
+// A operand read from tensor memory (lane = row, one column per TF32 element), B from shared memory
+__device__ __forceinline__ void umma_tf32_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "r"(tmem_a), "l"(bdesc), "r"(kIdesc), "r"(accumulate)
+        : "memory");
+}
+// 16 consecutive columns of this thread's lane <- 16 registers
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const float (&v)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+        "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+        "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+        "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+        "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15]))
+        : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -273,6 +293,247 @@ proj_gemm_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_constan
     }
 }
 
+
+// ================================================================================ pipelined version
+// The same product as proj_gemm_kernel with the phases of different K-blocks and tiles running at the
+// same time.  A CTA is persistent (one per SM, tiles dealt round-robin) and its warps have fixed roles
+// that talk through mbarriers over a ring of kStages operand stages and two accumulators:
+//   warp 8   producer: waits for a free stage, asks the TMA unit for A, B-hi, B-lo of the next K-block;
+//   warps 4-7 splitters: when a stage has landed, every thread reads ITS row of the A block from shared
+//            memory (the swizzle makes that conflict-free), splits it in registers and writes hi and lo
+//            into tensor memory (tcgen05.st), from where the MMAs take their A operand: the A block
+//            crosses shared memory once instead of being rewritten there twice and re-read three times;
+//   warp 9   issuer: when a stage is split, issues its 12 MMAs (A from tensor memory, B from shared
+//            memory); their completion frees the stage, and after a tile's last K-block hands the
+//            accumulator to the epilogue;
+//   warps 0-3 epilogue: read the finished accumulator (tcgen05.ld, warp w owns lanes 32w..32w+31), give it
+//            back as soon as it is in registers, then stage and store the rows.
+// So the copy of block k+2, the split of block k+1, the MMAs of block k and the store of the previous
+// tile overlap.  Every wait is bounded; a wait that gives up raises a CTA-wide abort flag that all roles
+// poll, so the CTA winds down together, frees its tensor memory and reports B200_ERR_TIMEOUT.
+constexpr int kStages = 4;
+constexpr int kStageBytes = 3 * kTileBytes;                       // A, B-hi, B-lo
+constexpr int kTmemAcc = 2 * kBN;                                 // two accumulators ...
+constexpr int kTmemCols = 512;                                    // ... then kStages x (32 hi + 32 lo) columns of A
+constexpr int kPatchBytes = 4 * 32 * 36 * 4;                      // epilogue staging, one patch per warp
+constexpr int kWsSmem = kStages * kStageBytes + kPatchBytes + 1024;
+constexpr int kWsThreads = 320;
+
+struct WsBars {
+    uint64_t full[kStages], ready[kStages], empty[kStages], acc_full[2], acc_empty[2];
+};
+
+__global__ void __launch_bounds__(kWsThreads, 1)
+proj_gemm_ws_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_constant__ CUtensorMap mapB1hi,
+                    const __grid_constant__ CUtensorMap mapB1lo, const __grid_constant__ CUtensorMap mapA2,
+                    const __grid_constant__ CUtensorMap mapB2hi, const __grid_constant__ CUtensorMap mapB2lo,
+                    const ProjArgs p) {
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ __align__(8) WsBars bars;
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ volatile int abort_flag;
+
+    const int tid = threadIdx.x, wid = tid >> 5, lane = tid & 31;
+    unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    auto stage_ptr = [&](int s, int which) -> float* { return reinterpret_cast<float*>(base + s * kStageBytes + which * kTileBytes); };
+    float* patches = reinterpret_cast<float*>(base + kStages * kStageBytes);
+
+    const long long n_tiles = (p.N + kBN - 1) / kBN, m_tiles = (p.M + kBM - 1) / kBM;
+    const long long tiles = n_tiles * m_tiles;
+    const int nkb = p.kb1 + p.kb2;
+
+    if (tid == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&bars.full[s], 1);
+            mbar_init(&bars.ready[s], 128);
+            mbar_init(&bars.empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&bars.acc_full[b], 1);
+            mbar_init(&bars.acc_empty[b], 128);
+        }
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (wid == 9) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_d = tmem_base_slot;
+    const uint32_t tmem_a = tmem_d + (uint32_t)kTmemAcc;  // A ring: stage s at columns s*64 (hi) and s*64+32 (lo)
+
+    // a bounded wait that also gives up when another role has raised the abort flag
+    auto wait = [&](uint64_t* bar, uint32_t parity) -> bool {
+        const uint32_t a = smem_u32(bar);
+        for (int i = 0; i < kWaitLimit; ++i) {
+            uint32_t ok;
+            asm volatile(
+                "{\n\t.reg .pred p;\n\t"
+                "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                "selp.u32 %0, 1, 0, p;\n\t}"
+                : "=r"(ok)
+                : "r"(a), "r"(parity)
+                : "memory");
+            if (ok) return true;
+            if (abort_flag) return false;
+            __nanosleep(32);
+        }
+        abort_flag = 1;
+        return false;
+    };
+
+    if (wid == 8) {
+        // ------------------------------------------------------------ producer (one lane)
+        if (lane == 0) {
+            long long it = 0;
+            for (long long t = blockIdx.x; t < tiles && !abort_flag; t += gridDim.x) {
+                const long long m_tile = t / n_tiles, n_tile = t - m_tile * n_tiles;
+                const int row0 = (int)(m_tile * kBM), col0 = (int)(n_tile * kBN);
+                for (int kb = 0; kb < nkb; ++kb, ++it) {
+                    const int s = (int)(it % kStages);
+                    const uint32_t ph = (uint32_t)((it / kStages) & 1);
+                    if (!wait(&bars.empty[s], ph ^ 1u)) break;  // a fresh barrier passes the wait for the phase before its first
+                    const bool first = kb < p.kb1;
+                    const int kx = (first ? kb : kb - p.kb1) * kBK;
+                    mbar_expect_tx(&bars.full[s], 3 * kTileBytes);
+                    tma_load_2d(stage_ptr(s, 0), first ? &mapA1 : &mapA2, kx, row0, &bars.full[s]);
+                    tma_load_2d(stage_ptr(s, 1), first ? &mapB1hi : &mapB2hi, kx, col0, &bars.full[s]);
+                    tma_load_2d(stage_ptr(s, 2), first ? &mapB1lo : &mapB2lo, kx, col0, &bars.full[s]);
+                }
+            }
+        }
+    } else if (wid == 9) {
+        // ------------------------------------------------------------ MMA issuer (one lane)
+        if (lane == 0) {
+            long long it = 0, ti = 0;
+            for (long long t = blockIdx.x; t < tiles && !abort_flag; t += gridDim.x, ++ti) {
+                const int buf = (int)(ti & 1);
+                if (!wait(&bars.acc_empty[buf], (uint32_t)(((ti >> 1) & 1) ^ 1))) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t acc = tmem_d + (uint32_t)(buf * kBN);
+                bool fine = true;
+                for (int kb = 0; kb < nkb; ++kb, ++it) {
+                    const int s = (int)(it % kStages);
+                    if (!wait(&bars.ready[s], (uint32_t)((it / kStages) & 1))) {
+                        fine = false;
+                        break;
+                    }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t aHi = tmem_a + (uint32_t)(s * 64), aLo = aHi + 32u;
+                    const uint64_t dBh = umma_desc_k_sw128(smem_u32(stage_ptr(s, 1))), dBl = umma_desc_k_sw128(smem_u32(stage_ptr(s, 2)));
+#pragma unroll
+                    for (int k = 0; k < kBK / 8; ++k) {  // 8 TF32 per MMA along K: 8 columns of A, 32 bytes of B
+                        const uint64_t adv = (uint64_t)(2 * k);
+                        umma_tf32_ts(acc, aLo + (uint32_t)(8 * k), dBh + adv, (kb | k) != 0);
+                        umma_tf32_ts(acc, aHi + (uint32_t)(8 * k), dBl + adv, 1u);
+                        umma_tf32_ts(acc, aHi + (uint32_t)(8 * k), dBh + adv, 1u);
+                    }
+                    umma_commit(&bars.empty[s]);  // the stage (shared and tensor memory) is free once these MMAs have read it
+                }
+                if (!fine) break;
+                umma_commit(&bars.acc_full[buf]);  // ... and the tile is complete once they have all finished
+            }
+        }
+    } else if (wid >= 4) {
+        // ------------------------------------------------------------ splitters (warps 4-7: lane quarter wid-4)
+        const int row = (wid - 4) * 32 + lane;  // this thread's row of the block = its tensor-memory lane
+        const uint32_t lane_field = (uint32_t)((wid - 4) * 32) << 16;
+        long long it = 0;
+        for (long long t = blockIdx.x; t < tiles && !abort_flag; t += gridDim.x) {
+            bool fine = true;
+            for (int kb = 0; kb < nkb; ++kb, ++it) {
+                const int s = (int)(it % kStages);
+                if (!wait(&bars.full[s], (uint32_t)((it / kStages) & 1))) {
+                    fine = false;
+                    break;
+                }
+                // row `row` of the 128-byte-swizzled block: its j-th 16-byte piece sits at piece j ^ (row % 8)
+                const float4* arow = reinterpret_cast<const float4*>(stage_ptr(s, 0)) + row * 8;
+                const uint32_t dst = tmem_a + lane_field + (uint32_t)(s * 64);
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    float hi[16], lo[16];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const float4 x = arow[(half * 4 + j) ^ (row & 7)];
+                        split_tf32(x.x, hi[4 * j], lo[4 * j]), split_tf32(x.y, hi[4 * j + 1], lo[4 * j + 1]);
+                        split_tf32(x.z, hi[4 * j + 2], lo[4 * j + 2]), split_tf32(x.w, hi[4 * j + 3], lo[4 * j + 3]);
+                    }
+                    tmem_st16(dst + (uint32_t)(half * 16), hi);
+                    tmem_st16(dst + 32u + (uint32_t)(half * 16), lo);
+                }
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&bars.ready[s])) : "memory");
+            }
+            if (!fine) break;
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue (warps 0-3)
+        float* patch = patches + wid * (32 * 36);
+        long long ti = 0;
+        for (long long t = blockIdx.x; t < tiles && !abort_flag; t += gridDim.x, ++ti) {
+            const long long m_tile = t / n_tiles, n_tile = t - m_tile * n_tiles;
+            const long long row0 = m_tile * kBM, col0 = n_tile * kBN;
+            const int buf = (int)(ti & 1);
+            if (!wait(&bars.acc_full[buf], (uint32_t)((ti >> 1) & 1))) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t acc = tmem_d + (uint32_t)(buf * kBN) + ((uint32_t)(wid * 32) << 16);
+#pragma unroll 1
+            for (int c = 0; c < kBN / 32; ++c) {
+                float v[32];
+                tmem_ld32(acc + (uint32_t)(c * 32), v);
+                if (c == kBN / 32 - 1) {  // the accumulator is in registers: hand it back before storing
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&bars.acc_empty[buf])) : "memory");
+                }
+#pragma unroll
+                for (int q = 0; q < 8; ++q)
+                    *reinterpret_cast<float4*>(patch + lane * 36 + q * 4) = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                __syncwarp();
+                const int cc = (lane & 7) * 4;
+#pragma unroll
+                for (int rr = 0; rr < 8; ++rr) {
+                    const int r = rr * 4 + (lane >> 3);
+                    const long long grow = row0 + wid * 32 + r, gcol = col0 + c * 32 + cc;
+                    if (grow < p.M && gcol < p.N) {
+                        float4 o = *reinterpret_cast<const float4*>(patch + r * 36 + cc);
+                        if (p.bias != nullptr) {
+                            o.x += p.bias[gcol];
+                            if (gcol + 1 < p.N) o.y += p.bias[gcol + 1];
+                            if (gcol + 2 < p.N) o.z += p.bias[gcol + 2];
+                            if (gcol + 3 < p.N) o.w += p.bias[gcol + 3];
+                        }
+                        float* dst = p.C + grow * p.ldc + gcol;
+                        if (gcol + 3 < p.N) {
+                            __stcs(reinterpret_cast<float4*>(dst), o);
+                        } else {
+                            const float ov[4] = {o.x, o.y, o.z, o.w};
+                            for (int e = 0; e < 4 && gcol + e < p.N; ++e) dst[e] = ov[e];
+                        }
+                    }
+                }
+                __syncwarp();
+            }
+        }
+    }
+    __syncwarp();  // the single-lane roles rejoin their warps before the CTA-wide barrier below
+    // wind down together; copies a producer has in flight get a bounded time to land before the CTA's
+    // shared memory is given up
+    if (abort_flag && tid == 0) {
+        atomicExch(&p.hdr->error, (unsigned int)B200_ERR_TIMEOUT);
+        for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (wid == 9) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(kTmemCols) : "memory");
+    }
+}
 
 // ================================================================================ weight gradient
 // dW[N, K] = G[M, N]^T * A[M, K]: the reduction runs over the tokens (rows of both operands), which are
@@ -517,6 +778,18 @@ static WgradPlan wgrad_plan(long long M, long long N, long long K) {
     return w;
 }
 
+static int sm_count_proj() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
 static bool row_ok(const void* p, long long ld) { return p != nullptr && ((uintptr_t)p & 15) == 0 && ld % 4 == 0; }
 
 }  // namespace b200
@@ -567,7 +840,8 @@ int b200_proj_gemm(int64_t M, int64_t N, int64_t K1, const void* A1, int64_t lda
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !configured[dev]) {
-        if (cudaFuncSetAttribute(proj_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem) != cudaSuccess)
+        if (cudaFuncSetAttribute(proj_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem) != cudaSuccess ||
+            cudaFuncSetAttribute(proj_gemm_ws_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kWsSmem) != cudaSuccess)
             return B200_ERR_LAUNCH;
         configured[dev] = true;
     }
@@ -575,7 +849,17 @@ int b200_proj_gemm(int64_t M, int64_t N, int64_t K1, const void* A1, int64_t lda
     a.C = (float*)C, a.bias = (const float*)bias, a.ldc = ldc, a.M = M, a.N = N;
     a.kb1 = (int)((K1 + kBK - 1) / kBK), a.kb2 = (int)((K2 + kBK - 1) / kBK);  // a ragged last block reads zeros past K
     a.hdr = reinterpret_cast<WsHeader*>(base);
+#ifdef PROJ_GEMM_SIMPLE
     proj_gemm_kernel<<<(unsigned int)tiles, 128, kGemmSmem, st>>>(mA1, mB1h, mB1l, mA2, mB2h, mB2l, a);
+#else
+    // few tiles: the one-tile-per-CTA kernel spreads them over more SMs than one persistent CTA per SM could
+    const long long sms = sm_count_proj();
+    if (tiles < 2 * sms) {
+        proj_gemm_kernel<<<(unsigned int)tiles, 128, kGemmSmem, st>>>(mA1, mB1h, mB1l, mA2, mB2h, mB2l, a);
+    } else {
+        proj_gemm_ws_kernel<<<(unsigned int)sms, kWsThreads, kWsSmem, st>>>(mA1, mB1h, mB1l, mA2, mB2h, mB2l, a);
+    }
+#endif
     return cudaGetLastError() == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
 }
 
