@@ -109,7 +109,38 @@ def _wrap_projections():
         mod.complex_in_proj, mod.real_out_proj = complex_in_proj, real_out_proj
 
 
+def _wrap_lru_forward():
+    """LRU.forward (``architectures/lru.py:85-110``) with its readout and feed-through as ONE product:
+    ``y = Re(C x) + D u`` is a single pass over ``y`` on the tensor-core GEMM (``proj_b200.readout``)
+    instead of a GEMM, a second GEMM and an addition.  Calls the fused path cannot take (CPU, other
+    dtypes, the "eager" backend, another backend preference) go to tsfast's own method."""
+    from . import proj_b200
+
+    lru = importlib.import_module("tsfast.models.architectures.lru")
+    if ("proj", "lru.forward") in _saved:
+        return
+    original = lru.LRU.forward
+
+    def forward(self, u, state=None, return_state=False):
+        if (self.backend != "scan" or _preference() not in ("auto", _KEY) or u.dtype != torch.float32 or not u.is_cuda
+                or proj_b200.supports(u, self.B_re) is not None or proj_b200.supports(u, self.D) is not None):
+            return original(self, u, state=state, return_state=return_state)
+        lam = self.eigenvalues()
+        gamma = torch.exp(self.gamma_log).unsqueeze(-1)
+        v = proj_b200.complex_in_proj(u, gamma * self.B_re, gamma * self.B_im)
+        x = lru.diagonal_recurrence(lam, v, state)
+        y = proj_b200.readout(x, self.C_re, self.C_im, u, self.D)
+        return (y, x[..., -1, :]) if return_state else y
+
+    forward.__doc__ = original.__doc__
+    _saved[("proj", "lru.forward")] = original
+    lru.LRU.forward = forward
+
+
 def _unwrap_projections():
+    original = _saved.pop(("proj", "lru.forward"), None)
+    if original is not None:
+        importlib.import_module("tsfast.models.architectures.lru").LRU.forward = original
     orig_in = _saved.pop(("proj", "complex_in_proj"), None)
     orig_out = _saved.pop(("proj", "real_out_proj"), None)
     if orig_in is None:
@@ -173,6 +204,7 @@ def install(fuse_dynonet: bool = False, fuse_projections: bool = False) -> list[
         done.append("dynonet.block")
     if fuse_projections:
         _wrap_projections()
+        _wrap_lru_forward()
         done.append("scan.projections")
     return done
 
