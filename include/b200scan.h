@@ -240,6 +240,31 @@ size_t b200_proj_wgrad_workspace_bytes(int64_t M, int64_t N, int64_t K);
 int b200_proj_wgrad(int64_t M, int64_t N, int64_t K, const void* G, int64_t ldg, const void* A, int64_t lda, void* dW,
                     int64_t lddw, void* workspace, size_t workspace_bytes, void* stream);
 
+/* ---- Pointwise glue of the LRU / S5 blocks (float32) -------------------------------------------
+ * LayerNorm over the last axis of x [M,D] (D <= 512): y = (x - mean) * rstd * gamma + beta with the
+ * biased variance and eps inside the square root, mean / rstd [M] saved for the adjoint; gamma and
+ * beta [D] may be NULL (1 and 0).  Replaces nn.LayerNorm in the pre-norm blocks,
+ * tsfast/models/architectures/lru.py:141,146 and s5.py:226,234 (PyTorch's kernel spends 0.38 ms on
+ * the [256000,128] rows of the full-model configuration, this one the time of one pass over HBM).
+ * Backward: g upstream gradient; writes dx [M,D] and, when not NULL, dgamma / dbeta [D]; the
+ * per-CTA partial rows in the workspace are added in a fixed order. */
+int b200_layernorm_fwd(int64_t M, int64_t D, const void* x, const void* gamma, const void* beta, float eps, void* y,
+                       void* mean, void* rstd, void* stream);
+size_t b200_layernorm_bwd_workspace_bytes(int64_t M, int64_t D);
+int b200_layernorm_bwd(int64_t M, int64_t D, const void* g, const void* x, const void* gamma, const void* mean,
+                       const void* rstd, void* dx, void* dgamma, void* dbeta, void* workspace, size_t workspace_bytes,
+                       void* stream);
+
+/* Gated residual out = u + a * sigmoid(b), all [M,D] with row pitches ldu/lda/ldb/ldo in floats (a and
+ * b may be the two halves of one [M,2D] tensor).  Replaces F.glu followed by the residual addition of
+ * the LRU block (lru.py:148-149) and the "half GLU" h * sigmoid(out2(h)) + u of the S5 block
+ * (s5.py:240-255) in one pass.  Backward: ga = g * sigmoid(b), gb = g * a * sigmoid(b) (1 - sigmoid(b));
+ * the gradient of u is g itself. */
+int b200_gated_residual_fwd(int64_t M, int64_t D, const void* u, int64_t ldu, const void* a, int64_t lda, const void* b,
+                            int64_t ldb, void* out, int64_t ldo, void* stream);
+int b200_gated_residual_bwd(int64_t M, int64_t D, const void* g, int64_t ldg, const void* a, int64_t lda, const void* b,
+                            int64_t ldb, void* ga, int64_t ldga, void* gb, int64_t ldgb, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

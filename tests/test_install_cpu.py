@@ -125,7 +125,7 @@ def test_projection_hooks_install_decline_on_cpu_and_restore(tsfast_models):
         assert "scan.projections" in slots
         assert lru.complex_in_proj is not scan.complex_in_proj and s5.real_out_proj is not scan.real_out_proj
         n = tsfast_b200.accelerate_linears(model)
-        assert n == 3  # encoder, GLU, decoder
+        assert n == 4  # encoder, LayerNorm, GLU, decoder
         assert torch.equal(model(u), want)
         assert tsfast_b200.restore_linears(model) == n
     finally:

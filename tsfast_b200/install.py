@@ -137,7 +137,53 @@ def _wrap_lru_forward():
     lru.LRU.forward = forward
 
 
+def _wrap_block_forwards():
+    """The bodies of LRUBlock / S5Block (``lru.py:145-152``, ``s5.py:233-257``) with the GLU (or the S5
+    "half GLU") and the residual addition as one pass (``glue_b200``).  Only when dropout is inactive
+    (it sits between the gate and the addition) and the tensors are float32 CUDA; otherwise tsfast's
+    own method runs."""
+    import torch.nn.functional as F
+
+    from . import glue_b200
+
+    lru = importlib.import_module("tsfast.models.architectures.lru")
+    s5 = importlib.import_module("tsfast.models.architectures.s5")
+    if ("glue", "lru.block") in _saved:
+        return
+    lru_orig, s5_orig = lru.LRUBlock.forward, s5.S5Block.forward
+
+    def _fusable(block, u):
+        return (u.is_cuda and u.dtype == torch.float32 and _preference() in ("auto", _KEY)
+                and not (block.training and block.dropout.p > 0))
+
+    def lru_block_forward(self, u, state=None, return_state=False):
+        if not _fusable(self, u):
+            return lru_orig(self, u, state=state, return_state=return_state)
+        h, new_state = self.lru(self.norm(u), state, return_state=True)
+        y = glue_b200.glu_residual(u, self.glu(F.gelu(h)))
+        return (y, new_state) if return_state else y
+
+    def s5_block_forward(self, u, state=None, return_state=False):
+        if not _fusable(self, u) or self.activation not in ("half_glu1", "half_glu2"):
+            return s5_orig(self, u, state=state, return_state=return_state)
+        h, new_state = self.s5(self.norm(u), state, return_state=True)
+        if self.activation == "half_glu1":
+            h = F.gelu(h)
+            y = glue_b200.gate_residual(u, h, self.out2(h))
+        else:
+            y = glue_b200.gate_residual(u, h, self.out2(F.gelu(h)))
+        return (y, new_state) if return_state else y
+
+    lru_block_forward.__doc__, s5_block_forward.__doc__ = lru_orig.__doc__, s5_orig.__doc__
+    _saved[("glue", "lru.block")], _saved[("glue", "s5.block")] = lru_orig, s5_orig
+    lru.LRUBlock.forward, s5.S5Block.forward = lru_block_forward, s5_block_forward
+
+
 def _unwrap_projections():
+    lru_orig, s5_orig = _saved.pop(("glue", "lru.block"), None), _saved.pop(("glue", "s5.block"), None)
+    if lru_orig is not None:
+        importlib.import_module("tsfast.models.architectures.lru").LRUBlock.forward = lru_orig
+        importlib.import_module("tsfast.models.architectures.s5").S5Block.forward = s5_orig
     original = _saved.pop(("proj", "lru.forward"), None)
     if original is not None:
         importlib.import_module("tsfast.models.architectures.lru").LRU.forward = original
@@ -150,27 +196,38 @@ def _unwrap_projections():
         mod.complex_in_proj, mod.real_out_proj = orig_in, orig_out
 
 
-def accelerate_linears(model) -> int:
-    """Give every ``nn.Linear`` inside ``model`` a forward on the tensor-core GEMM; returns how many.
+def accelerate_linears(model, norms: bool = True) -> int:
+    """Give every ``nn.Linear`` inside ``model`` a forward on the tensor-core GEMM and (with ``norms``)
+    every ``nn.LayerNorm`` over one axis a forward on ``glue_b200.layer_norm``; returns how many modules.
 
-    The replacement calls ``proj_b200.linear(x, weight, bias)`` whenever that kernel supports the
-    operands and ``F.linear`` otherwise (CPU tensors, other dtypes), so the module keeps working
-    everywhere.  Weights, biases and state dicts are not touched; ``restore_linears(model)`` removes the
-    per-instance forwards again."""
+    The replacements call the B200 kernels whenever these support the operands and ``F.linear`` /
+    ``F.layer_norm`` otherwise (CPU tensors, other dtypes, wide feature axes), so the modules keep
+    working everywhere.  Weights, biases and state dicts are not touched; ``restore_linears(model)``
+    removes the per-instance forwards again."""
     import torch.nn.functional as F
     from torch import nn
 
-    from . import proj_b200
+    from . import glue_b200, proj_b200
 
-    def fast_forward(self, x):
+    def fast_linear(self, x):
         if x.is_cuda and x.dtype == torch.float32 and proj_b200.supports(x, self.weight) is None:
             return proj_b200.linear(x, self.weight, self.bias)
         return F.linear(x, self.weight, self.bias)
 
+    def fast_norm(self, x):
+        if glue_b200.supports_norm(x, self.normalized_shape) is None:
+            return glue_b200.layer_norm(x, self.weight, self.bias, self.eps)
+        return F.layer_norm(x, self.normalized_shape, self.weight, self.bias, self.eps)
+
     count = 0
     for mod in model.modules():
-        if type(mod) is nn.Linear and "forward" not in mod.__dict__:
-            mod.forward = fast_forward.__get__(mod, nn.Linear)
+        if "forward" in mod.__dict__:
+            continue
+        if type(mod) is nn.Linear:
+            mod.forward = fast_linear.__get__(mod, nn.Linear)
+            count += 1
+        elif norms and type(mod) is nn.LayerNorm:
+            mod.forward = fast_norm.__get__(mod, nn.LayerNorm)
             count += 1
     return count
 
@@ -181,7 +238,7 @@ def restore_linears(model) -> int:
 
     count = 0
     for mod in model.modules():
-        if type(mod) is nn.Linear and "forward" in mod.__dict__:
+        if type(mod) in (nn.Linear, nn.LayerNorm) and "forward" in mod.__dict__:
             del mod.__dict__["forward"]
             count += 1
     return count
@@ -205,6 +262,7 @@ def install(fuse_dynonet: bool = False, fuse_projections: bool = False) -> list[
     if fuse_projections:
         _wrap_projections()
         _wrap_lru_forward()
+        _wrap_block_forwards()
         done.append("scan.projections")
     return done
 
