@@ -40,6 +40,8 @@ def test_golden():
 
 _SHAPES = [(2, 200, 64, 4), (3, 65, 20, 4), (1, 1, 8, 4), (2, 2, 12, 8), (2, 129, 33, 3), (1, 500, 512, 4), (4, 64, 256, 2)]
 _SHAPES += [(2, 70, 16, K) for K in range(2, 9)]
+# whole segments only: a segment that is first and last at once, several tiles per CTA of the persistent adjoint
+_SHAPES += [(1, 32, 8, 4), (2, 96, 300, 8), (3, 160, 130, 5), (700, 64, 256, 4)]
 
 
 @pytest.mark.parametrize("with_bias", [True, False])
