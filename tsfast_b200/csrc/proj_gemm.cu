@@ -320,9 +320,19 @@ constexpr int kWsSmem = kStages * kStageBytes + kPatchBytes + 1024;
 constexpr int kWsThreads = 320;
 
 struct WsBars {
-    uint64_t full[kStages], ready[kStages], empty[kStages], acc_full[2], acc_empty[2];
+    uint64_t full[kStages], ready[kStages], empty[kStages], acc_full[2], acc_empty[2], b_full;
 };
+#ifndef PROJ_RESIDENT
+#define PROJ_RESIDENT 1
+#endif
+constexpr int kResidentKb = 4;  // K-blocks of B (hi and lo) that fit beside the A ring: K <= 128
 
+// RESIDENT (K <= 128, one product): a CTA keeps ONE column tile for all its row tiles, so the split
+// weights of that tile (K/32 blocks of hi and lo, at most 128 KB) are fetched once and stay in shared
+// memory, and a stage of the ring carries the 16 KB A block alone: a third of the shared-memory fill
+// (measured: 4 % faster on 256 000 x 512 x 128; the rest of the shared-memory traffic, the three reads
+// of B by the MMAs and the epilogue's staging, is unchanged).
+template <bool RESIDENT>
 __global__ void __launch_bounds__(kWsThreads, 1)
 proj_gemm_ws_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_constant__ CUtensorMap mapB1hi,
                     const __grid_constant__ CUtensorMap mapB1lo, const __grid_constant__ CUtensorMap mapA2,
@@ -335,12 +345,28 @@ proj_gemm_ws_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_cons
 
     const int tid = threadIdx.x, wid = tid >> 5, lane = tid & 31;
     unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    auto stage_ptr = [&](int s, int which) -> float* { return reinterpret_cast<float*>(base + s * kStageBytes + which * kTileBytes); };
+    // streaming: stage s = {A, B-hi, B-lo} of one K-block; resident: B-hi/B-lo of K-block kb at the front,
+    // then a ring of A blocks
+    auto stage_ptr = [&](int s, int which) -> float* {
+        if constexpr (RESIDENT) return reinterpret_cast<float*>(base + (2 * kResidentKb + s) * kTileBytes);
+        else return reinterpret_cast<float*>(base + s * kStageBytes + which * kTileBytes);
+    };
+    auto resident_b = [&](int kb, int which) -> float* { return reinterpret_cast<float*>(base + (2 * kb + which) * kTileBytes); };
     float* patches = reinterpret_cast<float*>(base + kStages * kStageBytes);
 
     const long long n_tiles = (p.N + kBN - 1) / kBN, m_tiles = (p.M + kBM - 1) / kBM;
     const long long tiles = n_tiles * m_tiles;
     const int nkb = p.kb1 + p.kb2;
+    // the tiles of this CTA: streaming deals all tiles round-robin; resident keeps the column tile and
+    // strides over the row tiles (the grid is a multiple of n_tiles)
+    const long long t_begin = RESIDENT ? blockIdx.x / n_tiles : blockIdx.x;
+    const long long t_step = RESIDENT ? gridDim.x / n_tiles : gridDim.x;
+    const long long t_end = RESIDENT ? m_tiles : tiles;
+    const long long my_n = blockIdx.x % n_tiles;
+    auto decode = [&](long long t, long long& m_tile, long long& n_tile) {
+        if constexpr (RESIDENT) m_tile = t, n_tile = my_n;
+        else m_tile = t / n_tiles, n_tile = t - m_tile * n_tiles;
+    };
 
     if (tid == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -352,6 +378,7 @@ proj_gemm_ws_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_cons
             mbar_init(&bars.acc_full[b], 1);
             mbar_init(&bars.acc_empty[b], 128);
         }
+        mbar_init(&bars.b_full, 1);
         abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -390,8 +417,16 @@ proj_gemm_ws_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_cons
         // ------------------------------------------------------------ producer (one lane)
         if (lane == 0) {
             long long it = 0;
-            for (long long t = blockIdx.x; t < tiles && !abort_flag; t += gridDim.x) {
-                const long long m_tile = t / n_tiles, n_tile = t - m_tile * n_tiles;
+            if (RESIDENT && t_begin < t_end) {  // the column tile's split weights, once
+                mbar_expect_tx(&bars.b_full, 2 * nkb * kTileBytes);
+                for (int kb = 0; kb < nkb; ++kb) {
+                    tma_load_2d(resident_b(kb, 0), &mapB1hi, kb * kBK, (int)(my_n * kBN), &bars.b_full);
+                    tma_load_2d(resident_b(kb, 1), &mapB1lo, kb * kBK, (int)(my_n * kBN), &bars.b_full);
+                }
+            }
+            for (long long t = t_begin; t < t_end && !abort_flag; t += t_step) {
+                long long m_tile, n_tile;
+                decode(t, m_tile, n_tile);
                 const int row0 = (int)(m_tile * kBM), col0 = (int)(n_tile * kBN);
                 for (int kb = 0; kb < nkb; ++kb, ++it) {
                     const int s = (int)(it % kStages);
@@ -399,10 +434,12 @@ proj_gemm_ws_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_cons
                     if (!wait(&bars.empty[s], ph ^ 1u)) break;  // a fresh barrier passes the wait for the phase before its first
                     const bool first = kb < p.kb1;
                     const int kx = (first ? kb : kb - p.kb1) * kBK;
-                    mbar_expect_tx(&bars.full[s], 3 * kTileBytes);
+                    mbar_expect_tx(&bars.full[s], (RESIDENT ? 1 : 3) * kTileBytes);
                     tma_load_2d(stage_ptr(s, 0), first ? &mapA1 : &mapA2, kx, row0, &bars.full[s]);
-                    tma_load_2d(stage_ptr(s, 1), first ? &mapB1hi : &mapB2hi, kx, col0, &bars.full[s]);
-                    tma_load_2d(stage_ptr(s, 2), first ? &mapB1lo : &mapB2lo, kx, col0, &bars.full[s]);
+                    if constexpr (!RESIDENT) {
+                        tma_load_2d(stage_ptr(s, 1), first ? &mapB1hi : &mapB2hi, kx, col0, &bars.full[s]);
+                        tma_load_2d(stage_ptr(s, 2), first ? &mapB1lo : &mapB2lo, kx, col0, &bars.full[s]);
+                    }
                 }
             }
         }
@@ -410,7 +447,8 @@ proj_gemm_ws_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_cons
         // ------------------------------------------------------------ MMA issuer (one lane)
         if (lane == 0) {
             long long it = 0, ti = 0;
-            for (long long t = blockIdx.x; t < tiles && !abort_flag; t += gridDim.x, ++ti) {
+            if (RESIDENT && t_begin < t_end && !wait(&bars.b_full, 0)) abort_flag = 1;
+            for (long long t = t_begin; t < t_end && !abort_flag; t += t_step, ++ti) {
                 const int buf = (int)(ti & 1);
                 if (!wait(&bars.acc_empty[buf], (uint32_t)(((ti >> 1) & 1) ^ 1))) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -424,7 +462,8 @@ proj_gemm_ws_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_cons
                     }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t aHi = tmem_a + (uint32_t)(s * 64), aLo = aHi + 32u;
-                    const uint64_t dBh = umma_desc_k_sw128(smem_u32(stage_ptr(s, 1))), dBl = umma_desc_k_sw128(smem_u32(stage_ptr(s, 2)));
+                    const uint64_t dBh = umma_desc_k_sw128(smem_u32(RESIDENT ? resident_b(kb, 0) : stage_ptr(s, 1)));
+                    const uint64_t dBl = umma_desc_k_sw128(smem_u32(RESIDENT ? resident_b(kb, 1) : stage_ptr(s, 2)));
 #pragma unroll
                     for (int k = 0; k < kBK / 8; ++k) {  // 8 TF32 per MMA along K: 8 columns of A, 32 bytes of B
                         const uint64_t adv = (uint64_t)(2 * k);
@@ -443,7 +482,7 @@ proj_gemm_ws_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_cons
         const int row = (wid - 4) * 32 + lane;  // this thread's row of the block = its tensor-memory lane
         const uint32_t lane_field = (uint32_t)((wid - 4) * 32) << 16;
         long long it = 0;
-        for (long long t = blockIdx.x; t < tiles && !abort_flag; t += gridDim.x) {
+        for (long long t = t_begin; t < t_end && !abort_flag; t += t_step) {
             bool fine = true;
             for (int kb = 0; kb < nkb; ++kb, ++it) {
                 const int s = (int)(it % kStages);
@@ -476,8 +515,9 @@ proj_gemm_ws_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_cons
         // ------------------------------------------------------------ epilogue (warps 0-3)
         float* patch = patches + wid * (32 * 36);
         long long ti = 0;
-        for (long long t = blockIdx.x; t < tiles && !abort_flag; t += gridDim.x, ++ti) {
-            const long long m_tile = t / n_tiles, n_tile = t - m_tile * n_tiles;
+        for (long long t = t_begin; t < t_end && !abort_flag; t += t_step, ++ti) {
+            long long m_tile, n_tile;
+            decode(t, m_tile, n_tile);
             const long long row0 = m_tile * kBM, col0 = n_tile * kBN;
             const int buf = (int)(ti & 1);
             if (!wait(&bars.acc_full[buf], (uint32_t)((ti >> 1) & 1))) break;
@@ -841,7 +881,8 @@ int b200_proj_gemm(int64_t M, int64_t N, int64_t K1, const void* A1, int64_t lda
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !configured[dev]) {
         if (cudaFuncSetAttribute(proj_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem) != cudaSuccess ||
-            cudaFuncSetAttribute(proj_gemm_ws_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kWsSmem) != cudaSuccess)
+            cudaFuncSetAttribute(proj_gemm_ws_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kWsSmem) != cudaSuccess ||
+            cudaFuncSetAttribute(proj_gemm_ws_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kWsSmem) != cudaSuccess)
             return B200_ERR_LAUNCH;
         configured[dev] = true;
     }
@@ -853,11 +894,15 @@ int b200_proj_gemm(int64_t M, int64_t N, int64_t K1, const void* A1, int64_t lda
     proj_gemm_kernel<<<(unsigned int)tiles, 128, kGemmSmem, st>>>(mA1, mB1h, mB1l, mA2, mB2h, mB2l, a);
 #else
     // few tiles: the one-tile-per-CTA kernel spreads them over more SMs than one persistent CTA per SM could
-    const long long sms = sm_count_proj();
+    const long long sms = sm_count_proj(), n_tiles = (N + kBN - 1) / kBN;
     if (tiles < 2 * sms) {
         proj_gemm_kernel<<<(unsigned int)tiles, 128, kGemmSmem, st>>>(mA1, mB1h, mB1l, mA2, mB2h, mB2l, a);
+    } else if (PROJ_RESIDENT && a.kb2 == 0 && a.kb1 <= kResidentKb && n_tiles <= sms) {
+        // short K: the column tile's weights stay in shared memory; whole groups of n_tiles CTAs
+        const long long grid = sms - sms % n_tiles;
+        proj_gemm_ws_kernel<true><<<(unsigned int)grid, kWsThreads, kWsSmem, st>>>(mA1, mB1h, mB1l, mA2, mB2h, mB2l, a);
     } else {
-        proj_gemm_ws_kernel<<<(unsigned int)sms, kWsThreads, kWsSmem, st>>>(mA1, mB1h, mB1l, mA2, mB2h, mB2l, a);
+        proj_gemm_ws_kernel<false><<<(unsigned int)sms, kWsThreads, kWsSmem, st>>>(mA1, mB1h, mB1l, mA2, mB2h, mB2l, a);
     }
 #endif
     return cudaGetLastError() == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
