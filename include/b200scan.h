@@ -265,6 +265,15 @@ int b200_gated_residual_fwd(int64_t M, int64_t D, const void* u, int64_t ldu, co
 int b200_gated_residual_bwd(int64_t M, int64_t D, const void* g, int64_t ldg, const void* a, int64_t lda, const void* b,
                             int64_t ldb, void* ga, int64_t ldga, void* gb, int64_t ldgb, void* stream);
 
+/* Column sums out[c] = sum_m x[m,c] of a float32 matrix [M,D] (row pitch ldx floats, D <= 1024 when
+ * rows are 16-byte aligned, else D <= 256), added in a fixed order: the bias gradient of the linear
+ * layers around the scans (the `glu` / encoder / decoder nn.Linear of lru.py:142,197,201 and `out1` /
+ * `out2` / encoder / decoder of s5.py:229-230,302,318, whose autograd emits a column reduction of the
+ * output gradient).  M = 0 writes zeros. */
+size_t b200_colsum_workspace_bytes(int64_t M, int64_t D);
+int b200_colsum(int64_t M, int64_t D, const void* x, int64_t ldx, void* out, void* workspace, size_t workspace_bytes,
+                void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -93,3 +93,34 @@ def test_opcheck():
     torch.library.opcheck(gl._ln_op, (x, w, None, 1e-5), test_utils=("test_schema", "test_faketensor"))
     z = torch.randn(9, 48, device="cuda", requires_grad=True)
     torch.library.opcheck(gl._glu_res_op, (x, z), test_utils=("test_schema", "test_faketensor"))
+
+
+@pytest.mark.parametrize("M,D", [(1, 1), (5, 3), (1000, 128), (70001, 256), (4097, 512), (300, 1024), (9, 260), (333, 2000)])
+def test_column_sums_match_float64(M, D):
+    """Bias gradient of the linear layers: column sums in one pass, reproducible, any width."""
+    from tsfast_b200 import glue_b200
+    g = torch.randn(M, D, device="cuda")
+    got = glue_b200.column_sums(g)
+    want = g.double().sum(0)
+    assert torch.allclose(got.double(), want, rtol=1e-5, atol=1e-5 * float(want.abs().max() + 1))
+    assert torch.equal(got, glue_b200.column_sums(g))
+    # a strided view (the half of a wider matrix) and an expanded gradient
+    wide = torch.randn(M, 2 * D, device="cuda")
+    half = wide[:, D:]
+    assert torch.allclose(glue_b200.column_sums(half).double(), half.double().sum(0), rtol=1e-5,
+                          atol=1e-5 * float(half.abs().max() * M**0.5 + 1))
+    ones = torch.ones(1, D, device="cuda").expand(M, D)
+    assert torch.allclose(glue_b200.column_sums(ones), torch.full((D,), float(M), device="cuda"))
+
+
+def test_linear_bias_gradient_uses_the_column_sum_kernel():
+    from tsfast_b200 import glue_b200, proj_b200
+
+    a = torch.randn(3000, 64, device="cuda", requires_grad=True)
+    w = torch.randn(96, 64, device="cuda", requires_grad=True)
+    b = torch.randn(96, device="cuda", requires_grad=True)
+    g = torch.randn(3000, 96, device="cuda")
+    before = glue_b200.calls
+    proj_b200.linear(a, w, b).backward(g)
+    assert glue_b200.calls == before + 1
+    assert torch.allclose(b.grad.double(), g.double().sum(0), rtol=1e-5, atol=1e-4)

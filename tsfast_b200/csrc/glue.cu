@@ -5,7 +5,7 @@
 // feature axis is short (tens to a few hundred), so every kernel is one pass over HBM:
 //   * LayerNorm: one warp per row, the row held in registers (two-pass mean / variance, as PyTorch
 //     computes it), statistics saved for the adjoint; the adjoint adds the weight / bias gradients of
-//     a CTA's rows in shared memory and writes one partial row per CTA, which ln_param_reduce_kernel
+//     a CTA's rows in shared memory and writes one partial row per CTA, which rows_reduce_kernel
 //     sums in a fixed order (no atomics, reproducible);
 //   * gated residual: elementwise, four features per thread.
 #include "common.cuh"
@@ -124,16 +124,90 @@ __global__ void __launch_bounds__(256) layernorm_bwd_kernel(const float* __restr
     }
 }
 
-// out[which][c] = sum over CTAs (ascending) of part[cta][which][c]
-__global__ void ln_param_reduce_kernel(const float* __restrict__ part, int ctas, int D, float* __restrict__ dgamma,
-                                       float* __restrict__ dbeta) {
-    const int e = blockIdx.x * blockDim.x + threadIdx.x;
-    if (e >= 2 * D) return;
-    const int which = e / D, c = e - which * D;
+// out[e] = sum over partial rows of part[row][e], e in [0, width), in a fixed order: 32 lanes per
+// output each add every 32nd partial (eight independent loads per round), then the 32 sub-sums are
+// added in lane order; 32 outputs per block keep the reads of one partial row coalesced.  Entries
+// below `split` go to out0, the rest to out1 (either may be null).
+__global__ void __launch_bounds__(1024) rows_reduce_kernel(const float* __restrict__ part, int rows, int width, int split,
+                                                           float* __restrict__ out0, float* __restrict__ out1) {
+    __shared__ float sh[32][33];
+    const int o = threadIdx.x & 31, pl = threadIdx.x >> 5;
+    const int e = blockIdx.x * 32 + o;
+    const bool live = e < width;
+    const long long stride = width;
     float s = 0.f;
-    for (int k = 0; k < ctas; ++k) s += part[((long long)k * 2 + which) * D + c];
-    float* dst = which == 0 ? dgamma : dbeta;
-    if (dst != nullptr) dst[c] = s;
+    if (live) {
+        int k = pl;
+        for (; k + 224 < rows; k += 256) {
+            float v[8];
+#pragma unroll
+            for (int r = 0; r < 8; ++r) v[r] = part[(k + 32 * r) * stride + e];
+#pragma unroll
+            for (int r = 0; r < 8; ++r) s += v[r];
+        }
+        for (; k < rows; k += 32) s += part[k * stride + e];
+    }
+    sh[pl][o] = s;
+    __syncthreads();
+    if (pl == 0 && live) {
+        float t = 0.f;
+#pragma unroll
+        for (int q = 0; q < 32; ++q) t += sh[q][o];
+        float* dst = e < split ? out0 : out1;
+        if (dst != nullptr) dst[e < split ? e : e - split] = t;
+    }
+}
+
+// ------------------------------------------------------------------------------- column sums
+// out[c] = sum over rows of x[m, c] (the bias gradient of a linear layer).  A CTA owns a contiguous
+// slab of rows; a thread owns VEC neighbouring columns and every (256 / threads-per-row)-th row of
+// the slab, eight rows in flight; the CTA's row groups are added in shared memory in a fixed order and
+// one partial row per CTA goes to the workspace, which colsum_reduce_kernel adds in a fixed order.
+template <int VEC>
+__global__ void __launch_bounds__(256) colsum_kernel(const float* __restrict__ x, long long ldx, long long M, int D,
+                                                     long long rows_per_cta, float* __restrict__ part) {
+    extern __shared__ float sh[];  // [groups][D]
+    const int tpr = (D + VEC - 1) / VEC;          // threads per row
+    const int groups = 256 / tpr;                 // row groups of the CTA (>= 1: D <= 256 * VEC)
+    const int grp = threadIdx.x / tpr, c = (threadIdx.x - grp * tpr) * VEC;
+    const long long r0 = (long long)blockIdx.x * rows_per_cta;
+    const long long r1 = r0 + rows_per_cta < M ? r0 + rows_per_cta : M;
+    float acc[VEC];
+#pragma unroll
+    for (int q = 0; q < VEC; ++q) acc[q] = 0.f;
+    if (grp < groups) {
+        long long r = r0 + grp;
+        for (; r + 7LL * groups < r1; r += 8LL * groups) {
+            float v[8][VEC];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float* p = x + (r + (long long)i * groups) * ldx + c;
+                if constexpr (VEC == 4) {
+                    const float4 t = __ldcs(reinterpret_cast<const float4*>(p));
+                    v[i][0] = t.x, v[i][1] = t.y, v[i][2] = t.z, v[i][3] = t.w;
+                } else {
+                    v[i][0] = __ldcs(p);
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+#pragma unroll
+                for (int q = 0; q < VEC; ++q) acc[q] += v[i][q];
+        }
+        for (; r < r1; r += groups) {
+            const float* p = x + r * ldx + c;
+#pragma unroll
+            for (int q = 0; q < VEC; ++q) acc[q] += p[q];
+        }
+#pragma unroll
+        for (int q = 0; q < VEC; ++q) sh[grp * D + c + q] = acc[q];
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < D; e += 256) {
+        float s = 0.f;
+        for (int g = 0; g < groups; ++g) s += sh[g * D + e];
+        part[(long long)blockIdx.x * D + e] = s;
+    }
 }
 
 // ------------------------------------------------------------------------------- gated residual
@@ -201,6 +275,12 @@ static int ln_bwd_ctas(long long M) {
     return (int)(want < cap ? (want < 1 ? 1 : want) : cap);
 }
 static bool vec4(const void* p, long long ld) { return ((uintptr_t)p & 15) == 0 && ld % 4 == 0; }
+// CTAs of the column-sum kernel: every SM several times over, but at least 64 rows per CTA
+static int colsum_ctas(long long M) {
+    long long want = (M + 63) / 64;
+    const long long cap = 148 * 8;
+    return (int)(want < cap ? (want < 1 ? 1 : want) : cap);
+}
 
 }  // namespace b200
 
@@ -265,8 +345,38 @@ int b200_layernorm_bwd(int64_t M, int64_t D, const void* g, const void* x, const
     }
 #undef LN_BWD
     if (cudaGetLastError() != cudaSuccess) return B200_ERR_LAUNCH;
-    ln_param_reduce_kernel<<<(unsigned int)((2 * D + 255) / 256), 256, 0, st>>>((const float*)workspace, ctas, (int)D, (float*)dgamma,
-                                                                                 (float*)dbeta);
+    rows_reduce_kernel<<<(unsigned int)((2 * D + 31) / 32), 1024, 0, st>>>((const float*)workspace, ctas, 2 * (int)D, (int)D,
+                                                                           (float*)dgamma, (float*)dbeta);
+    return cudaGetLastError() == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
+}
+
+size_t b200_colsum_workspace_bytes(int64_t M, int64_t D) {
+    if (M <= 0 || D <= 0) return 256;
+    return b200::align_up(sizeof(float) * (size_t)D * (size_t)b200::colsum_ctas(M), 256);
+}
+
+int b200_colsum(int64_t M, int64_t D, const void* x, int64_t ldx, void* out, void* workspace, size_t workspace_bytes,
+                void* stream) {
+    using namespace b200;
+    if (M < 0 || D < 1 || !out) return B200_ERR_ARG;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (M == 0) return cudaMemsetAsync(out, 0, sizeof(float) * D, st) == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
+    if (!x || ldx < D) return B200_ERR_ARG;
+    const bool v4 = D % 4 == 0 && vec4(x, ldx);
+    if (D > 256 * (v4 ? 4 : 1)) return B200_ERR_UNSUPPORTED;
+    if (!workspace || ((uintptr_t)workspace % 256) != 0 || workspace_bytes < b200_colsum_workspace_bytes(M, D))
+        return B200_ERR_WORKSPACE;
+    const int ctas = colsum_ctas(M);
+    const long long rows_per_cta = (M + ctas - 1) / ctas;
+    const int tpr = (int)(v4 ? D / 4 : D), groups = 256 / tpr;
+    const size_t smem = sizeof(float) * (size_t)groups * (size_t)D;
+    if (v4)
+        colsum_kernel<4><<<ctas, 256, smem, st>>>((const float*)x, ldx, M, (int)D, rows_per_cta, (float*)workspace);
+    else
+        colsum_kernel<1><<<ctas, 256, smem, st>>>((const float*)x, ldx, M, (int)D, rows_per_cta, (float*)workspace);
+    if (cudaGetLastError() != cudaSuccess) return B200_ERR_LAUNCH;
+    rows_reduce_kernel<<<(unsigned int)((D + 31) / 32), 1024, 0, st>>>((const float*)workspace, ctas, (int)D, (int)D, (float*)out,
+                                                                       nullptr);
     return cudaGetLastError() == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
 }
 

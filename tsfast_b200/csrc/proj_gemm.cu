@@ -735,15 +735,27 @@ proj_wgrad_kernel(const __grid_constant__ CUtensorMap mapG, const __grid_constan
     }
 }
 
-// dW[n][k] = sum over slices of part[s][n][k], slices in ascending order (fixed, so reproducible)
+// dW[n][k] = sum over slices of part[s][n][k] in a fixed order (reproducible)
 __global__ void wgrad_reduce_kernel(const float* __restrict__ part, int splits, long long N, long long K, long long Kp,
                                     float* __restrict__ dW, long long lddw) {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= N * K) return;
     const long long n = i / K, k = i - n * K;
-    float s = 0.f;
-    for (int sp = 0; sp < splits; ++sp) s += part[((long long)sp * N + n) * Kp + k];
-    dW[n * lddw + k] = s;
+    // eight running sums (slice sp goes to sum sp % 8) so that many loads are in flight; the sums are
+    // then added in a fixed tree
+    const float* src = part + n * Kp + k;
+    const long long stride = N * Kp;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    int sp = 0;
+#pragma unroll 2
+    for (; sp + 8 <= splits; sp += 8) {
+#pragma unroll
+        for (int r = 0; r < 8; ++r) acc[r] += src[(long long)(sp + r) * stride];
+    }
+#pragma unroll
+    for (int r = 0; r < 8; ++r)
+        if (sp + r < splits) acc[r] += src[(long long)(sp + r) * stride];
+    dW[n * lddw + k] = ((acc[0] + acc[1]) + (acc[2] + acc[3])) + ((acc[4] + acc[5]) + (acc[6] + acc[7]));
 }
 
 // ------------------------------------------------------------------------------- host side

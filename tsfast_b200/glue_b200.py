@@ -8,6 +8,8 @@ of a block.  This module provides
 * ``layer_norm(x, weight, bias, eps)`` – ``F.layer_norm`` over the last axis (width up to 512);
 * ``glu_residual(u, z)``               – ``u + F.glu(z, dim=-1)``;
 * ``gate_residual(u, a, b)``           – ``u + a * sigmoid(b)``;
+* ``column_sums(g)``                   – ``g.sum(0)`` of a ``[M, D]`` matrix in a fixed order (the bias
+  gradient of the linear layers; no autograd of its own);
 
 each a custom op pair (forward, adjoint) on ``libb200scan.so`` with fake implementations.
 ``tsfast_b200.accelerate_linears(model)`` routes a model's ``nn.LayerNorm`` modules here and
@@ -20,7 +22,7 @@ import torch
 
 from . import _lib
 
-__all__ = ["layer_norm", "glu_residual", "gate_residual", "supports_norm", "calls"]
+__all__ = ["layer_norm", "glu_residual", "gate_residual", "column_sums", "supports_norm", "calls"]
 
 calls = 0  # launches through this module since import (the drop-in tests read it)
 _MAX_WIDTH = 512
@@ -28,6 +30,35 @@ _MAX_WIDTH = 512
 
 def _cuda_f32(*ts) -> bool:
     return all(t is None or (t.is_cuda and t.dtype == torch.float32) for t in ts)
+
+
+@torch.library.custom_op("b200scan::column_sums", mutates_args=())
+def _colsum_op(g: torch.Tensor) -> torch.Tensor:
+    global calls
+    if not _cuda_f32(g) or g.dim() != 2:
+        raise RuntimeError("b200scan::column_sums: needs a float32 CUDA matrix [M, D]")
+    m, d = g.shape
+    if (d > 1 and g.stride(1) != 1) or (m > 1 and g.stride(0) < d):
+        g = g.contiguous()  # expanded or transposed views
+    if d > (1024 if (g.data_ptr() % 16 == 0 and (m < 2 or g.stride(0) % 4 == 0) and d % 4 == 0) else 256):
+        return g.sum(0)  # wider than the kernel's row groups: PyTorch's reduction, same device
+    out = g.new_empty(d)
+    L_ = _lib.lib()
+    ws = _lib.workspace(L_.b200_colsum_workspace_bytes(m, d), g.device)
+    calls += 1
+    _lib.check(L_.b200_colsum(m, d, _lib.ptr(g), g.stride(0) if m > 1 else d, _lib.ptr(out), _lib.ptr(ws), ws.numel(),
+                              _lib.stream_ptr(g.device)), "b200_colsum")
+    return out
+
+
+@_colsum_op.register_fake
+def _(g):
+    return g.new_empty(g.shape[1])
+
+
+def column_sums(g: torch.Tensor) -> torch.Tensor:
+    """``g.sum(0)`` for a float32 CUDA matrix, one pass over HBM, summed in a fixed order."""
+    return _colsum_op(g)
 
 
 def supports_norm(x: torch.Tensor, normalized_shape) -> str | None:

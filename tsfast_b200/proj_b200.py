@@ -23,7 +23,7 @@ from __future__ import annotations
 
 import torch
 
-from . import _lib
+from . import _lib, glue_b200
 
 __all__ = ["linear", "complex_in_proj", "real_out_proj", "readout", "supports", "calls"]
 
@@ -161,7 +161,7 @@ def _adjoint(ctx, g):
     need = ctx.needs_input_grad
     ga = _input_grad(g, w) if need[0] else None
     gw = _proj_wgrad_op(g, a) if need[1] else None
-    gb = g.sum(0) if (bias is not None and need[2]) else None
+    gb = glue_b200.column_sums(g) if (bias is not None and need[2]) else None
     return ga, gw, gb
 
 
