@@ -274,6 +274,32 @@ size_t b200_colsum_workspace_bytes(int64_t M, int64_t D);
 int b200_colsum(int64_t M, int64_t D, const void* x, int64_t ldx, void* out, void* workspace, size_t workspace_bytes,
                 void* stream);
 
+/* Parameter prologues of the LRU and S5 layers: from the stored parameters to what the projection GEMM
+ * and the scan consume, one launch forward and one for the adjoint (PyTorch runs a dozen tiny kernels
+ * forward and twice that backward, per layer and step).
+ *   LRU (LRU.eigenvalues and the gamma scaling in LRU.forward, lru.py:79-83,97-99):
+ *     lam[j] = exp(-exp(nu_log[j])) * exp(i exp(theta_log[j]))                      complex64 [n]
+ *     W[2j] = exp(gamma_log[j]) B_re[j],  W[2j+1] = exp(gamma_log[j]) B_im[j]       float32 [2n, d]
+ *   S5 (S5.discretize, s5.py:154-170; mode 0 "zoh", 1 "bilinear"; clip_eigs clamps Lambda_re to <= -1e-4;
+ *   step = step_rescale * exp(log_step)):
+ *     lam_bar[j] complex64 [p],  W[2j] + i W[2j+1] = B_bar[j] = c_j (B_re[j] + i B_im[j])   float32 [2p, d]
+ * W is the input-projection weight with interleaved (re, im) rows: u W^T has the memory layout of the
+ * complex [.., n] tensor complex_in_proj returns (_core/scan.py:272-292).  The adjoint takes the
+ * gradients of lam / lam_bar (complex64, PyTorch's convention) and of W (either may be null = zero)
+ * and writes the gradient of every parameter. */
+int b200_lru_prologue_fwd(int64_t n, int64_t d, const void* nu_log, const void* theta_log, const void* gamma_log,
+                          const void* B_re, const void* B_im, void* lam, void* W, void* stream);
+int b200_lru_prologue_bwd(int64_t n, int64_t d, const void* nu_log, const void* theta_log, const void* gamma_log,
+                          const void* B_re, const void* B_im, const void* glam, const void* gW, void* g_nu, void* g_theta,
+                          void* g_gamma, void* gB_re, void* gB_im, void* stream);
+int b200_s5_discretize_fwd(int64_t p, int64_t d, int mode, int clip_eigs, float step_rescale, const void* Lambda_re,
+                           const void* Lambda_im, const void* log_step, const void* B_re, const void* B_im, void* lam_bar,
+                           void* W, void* stream);
+int b200_s5_discretize_bwd(int64_t p, int64_t d, int mode, int clip_eigs, float step_rescale, const void* Lambda_re,
+                           const void* Lambda_im, const void* log_step, const void* B_re, const void* B_im,
+                           const void* glam_bar, const void* gW, void* gLambda_re, void* gLambda_im, void* g_log_step,
+                           void* gB_re, void* gB_im, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -58,6 +58,10 @@ SIGNATURES = {
     "b200_layernorm_bwd": (_int, [_i64, _i64] + [_vp] * 9 + [_sz, _vp]),
     "b200_gated_residual_fwd": (_int, [_i64, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp]),
     "b200_gated_residual_bwd": (_int, [_i64, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp]),
+    "b200_lru_prologue_fwd": (_int, [_i64, _i64] + [_vp] * 8),
+    "b200_lru_prologue_bwd": (_int, [_i64, _i64] + [_vp] * 13),
+    "b200_s5_discretize_fwd": (_int, [_i64, _i64, _int, _int, ctypes.c_float] + [_vp] * 8),
+    "b200_s5_discretize_bwd": (_int, [_i64, _i64, _int, _int, ctypes.c_float] + [_vp] * 13),
     "b200_colsum_workspace_bytes": (_sz, [_i64, _i64]),
     "b200_colsum": (_int, [_i64, _i64, _vp, _i64, _vp, _vp, _sz, _vp]),
     "b200_conv_silu_fwd": (_int, [_i64] * 4 + [_vp, _i64, _i64] + [_vp] * 5),

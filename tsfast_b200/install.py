@@ -110,31 +110,47 @@ def _wrap_projections():
 
 
 def _wrap_lru_forward():
-    """LRU.forward (``architectures/lru.py:85-110``) with its readout and feed-through as ONE product:
+    """LRU.forward (``architectures/lru.py:85-110``) and S5.forward (``s5.py:172-200``) with their parameter
+    prologues as one launch (``prologue_b200``), and the LRU readout and feed-through as ONE product:
     ``y = Re(C x) + D u`` is a single pass over ``y`` on the tensor-core GEMM (``proj_b200.readout``)
     instead of a GEMM, a second GEMM and an addition.  Calls the fused path cannot take (CPU, other
     dtypes, the "eager" backend, another backend preference) go to tsfast's own method."""
-    from . import proj_b200
+    from . import prologue_b200, proj_b200
 
     lru = importlib.import_module("tsfast.models.architectures.lru")
+    s5 = importlib.import_module("tsfast.models.architectures.s5")
     if ("proj", "lru.forward") in _saved:
         return
-    original = lru.LRU.forward
+    original, s5_original = lru.LRU.forward, s5.S5.forward
+
+    def _fusable(layer, u, *weights):
+        return (layer.backend == "scan" and _preference() in ("auto", _KEY) and u.dtype == torch.float32 and u.is_cuda
+                and all(proj_b200.supports(u, w) is None for w in weights))
 
     def forward(self, u, state=None, return_state=False):
-        if (self.backend != "scan" or _preference() not in ("auto", _KEY) or u.dtype != torch.float32 or not u.is_cuda
-                or proj_b200.supports(u, self.B_re) is not None or proj_b200.supports(u, self.D) is not None):
+        if not _fusable(self, u, self.B_re, self.D):
             return original(self, u, state=state, return_state=return_state)
-        lam = self.eigenvalues()
-        gamma = torch.exp(self.gamma_log).unsqueeze(-1)
-        v = proj_b200.complex_in_proj(u, gamma * self.B_re, gamma * self.B_im)
-        x = lru.diagonal_recurrence(lam, v, state)
+        # eigenvalues and the gamma-scaled, interleaved input weight in one launch (lru.py:79-83, 97-99)
+        lam, W = prologue_b200.lru_prologue(self.nu_log, self.theta_log, self.gamma_log, self.B_re, self.B_im)
+        x = lru.diagonal_recurrence(lam, proj_b200.packed_in_proj(u, W), state)
         y = proj_b200.readout(x, self.C_re, self.C_im, u, self.D)
         return (y, x[..., -1, :]) if return_state else y
 
-    forward.__doc__ = original.__doc__
-    _saved[("proj", "lru.forward")] = original
-    lru.LRU.forward = forward
+    def s5_forward(self, u, state=None, return_state=False):
+        if not _fusable(self, u, self.B_re) or self.discretization not in ("zoh", "bilinear"):
+            return s5_original(self, u, state=state, return_state=return_state)
+        # S5.discretize (s5.py:154-170) and the interleaving of B_bar in one launch
+        lam_bar, W = prologue_b200.s5_discretize(self.Lambda_re, self.Lambda_im, self.log_step, self.B_re, self.B_im,
+                                                 discretization=self.discretization, clip_eigs=self.clip_eigs,
+                                                 step_rescale=self.step_rescale)
+        x = s5.diagonal_recurrence(lam_bar, proj_b200.packed_in_proj(u, W), state)
+        C_re, C_im = (2 * self.C_re, 2 * self.C_im) if self.conj_sym else (self.C_re, self.C_im)
+        y = proj_b200.real_out_proj(x, C_re, C_im) + self.D * u
+        return (y, x[..., -1, :]) if return_state else y
+
+    forward.__doc__, s5_forward.__doc__ = original.__doc__, s5_original.__doc__
+    _saved[("proj", "lru.forward")], _saved[("proj", "s5.forward")] = original, s5_original
+    lru.LRU.forward, s5.S5.forward = forward, s5_forward
 
 
 def _wrap_block_forwards():
@@ -184,9 +200,10 @@ def _unwrap_projections():
     if lru_orig is not None:
         importlib.import_module("tsfast.models.architectures.lru").LRUBlock.forward = lru_orig
         importlib.import_module("tsfast.models.architectures.s5").S5Block.forward = s5_orig
-    original = _saved.pop(("proj", "lru.forward"), None)
+    original, s5_original = _saved.pop(("proj", "lru.forward"), None), _saved.pop(("proj", "s5.forward"), None)
     if original is not None:
         importlib.import_module("tsfast.models.architectures.lru").LRU.forward = original
+        importlib.import_module("tsfast.models.architectures.s5").S5.forward = s5_original
     orig_in = _saved.pop(("proj", "complex_in_proj"), None)
     orig_out = _saved.pop(("proj", "real_out_proj"), None)
     if orig_in is None:

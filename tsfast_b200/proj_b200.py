@@ -25,7 +25,7 @@ import torch
 
 from . import _lib, glue_b200
 
-__all__ = ["linear", "complex_in_proj", "real_out_proj", "readout", "supports", "calls"]
+__all__ = ["linear", "complex_in_proj", "packed_in_proj", "real_out_proj", "readout", "supports", "calls"]
 
 calls = 0  # launches through this module since import (the drop-in tests read it)
 
@@ -189,6 +189,12 @@ def complex_in_proj(u: torch.Tensor, W_re: torch.Tensor, W_im: torch.Tensor) -> 
     n, d = W_re.shape
     w = torch.stack((W_re, W_im), dim=1).reshape(2 * n, d)
     return torch.view_as_complex(linear(u, w).unflatten(-1, (n, 2)))
+
+
+def packed_in_proj(u: torch.Tensor, W: torch.Tensor) -> torch.Tensor:
+    """``complex_in_proj`` for a weight that already has the interleaved (re, im) row order ``[2n, d]``
+    (what ``prologue_b200`` produces): real ``u [..., d]`` -> complex ``[..., n]``."""
+    return torch.view_as_complex(linear(u, W).unflatten(-1, (W.shape[0] // 2, 2)))
 
 
 def _readout_weight(W_re, W_im):
