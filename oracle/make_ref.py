@@ -29,8 +29,8 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 DEST = HERE / "_ref"
 
-# the reference's tests of the scan path (SURVEY of the hot path: scans, their backends, dispatch,
-# and the four model families that call them)
+# the reference's tests of the scan path: the scans, their backends, dispatch, and the four model
+# families that call them
 HOT_PATH_TESTS = [
     "conftest.py",
     "test_scan.py",

@@ -255,10 +255,9 @@ def test_tsfast_own_test_files_pass_with_b200_installed(tmp_path):
     tail = (r.stdout + r.stderr)[-4000:]
     assert report.exists(), tail
     rep = json.loads(report.read_text())
-    out_dir = ROOT / "gpurun_out"
-    if out_dir.is_dir():
+    if os.environ.get("B200_REPORT_DIR") and Path(os.environ["B200_REPORT_DIR"]).is_dir():  # keep the record as files
+        out_dir = Path(os.environ["B200_REPORT_DIR"])
         (out_dir / "reference_tests_with_b200.json").write_text(json.dumps(rep, indent=1))
-    if out_dir.is_dir():
         (out_dir / "reference_tests_with_b200.log").write_text((r.stdout + r.stderr)[-60000:])
     assert rep["failed"] == 0 and r.returncode == 0, (rep, tail)
     assert rep["passed"] > 100
