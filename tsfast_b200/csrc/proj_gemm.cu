@@ -41,6 +41,7 @@ struct ProjArgs {
     long long ldc;
     long long M, N;
     int kb1, kb2;  // K-blocks of the first and of the second product
+    int tma_c;     // C rows are 16-byte aligned: the pipelined kernel stores it with TMA
     WsHeader* hdr;
 };
 
@@ -76,6 +77,20 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
         "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
         : "memory");
 }
+// TMA store of a [rows x 32 floats] box from (128-byte-swizzled) shared memory; rows and columns past
+// the end of the tensor are clipped.  Bulk stores are tracked per issuing thread in groups.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* src, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(map), "r"(x), "r"(y),
+                 "r"(smem_u32(src))
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() {  // at most N of this thread's store groups still reading shared memory
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 // Shared-memory matrix descriptor of a K-major operand block in the 128-byte-swizzled layout: rows of
 // 128 bytes, groups of 8 rows 1024 bytes apart (stride byte offset), descriptor version 1 (sm_100).
 __device__ __forceinline__ uint64_t umma_desc_k_sw128(uint32_t saddr) {
@@ -307,7 +322,9 @@ proj_gemm_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_constan
 //            memory); their completion frees the stage, and after a tile's last K-block hands the
 //            accumulator to the epilogue;
 //   warps 0-3 epilogue: read the finished accumulator (tcgen05.ld, warp w owns lanes 32w..32w+31), give it
-//            back as soon as it is in registers, then stage and store the rows.
+//            back as soon as it is in registers, add the bias, write 32 x 32 patches into shared memory
+//            (128-byte swizzle, two patches alternating) and hand each to the TMA unit, which stores it
+//            while the next one is being filled (rows not 16-byte aligned: plain row stores instead).
 // So the copy of block k+2, the split of block k+1, the MMAs of block k and the store of the previous
 // tile overlap.  Every wait is bounded; a wait that gives up raises a CTA-wide abort flag that all roles
 // poll, so the CTA winds down together, frees its tensor memory and reports B200_ERR_TIMEOUT.
@@ -315,7 +332,7 @@ constexpr int kStages = 4;
 constexpr int kStageBytes = 3 * kTileBytes;                       // A, B-hi, B-lo
 constexpr int kTmemAcc = 2 * kBN;                                 // two accumulators ...
 constexpr int kTmemCols = 512;                                    // ... then kStages x (32 hi + 32 lo) columns of A
-constexpr int kPatchBytes = 4 * 32 * 36 * 4;                      // epilogue staging, one patch per warp
+constexpr int kPatchBytes = 4 * 2 * 32 * 32 * 4;                  // epilogue staging: two 32 x 32 patches per warp
 constexpr int kWsSmem = kStages * kStageBytes + kPatchBytes + 1024;
 constexpr int kWsThreads = 320;
 
@@ -324,6 +341,9 @@ struct WsBars {
 };
 #ifndef PROJ_RESIDENT
 #define PROJ_RESIDENT 1
+#endif
+#ifndef PROJ_TMA_STORE
+#define PROJ_TMA_STORE 1
 #endif
 constexpr int kResidentKb = 4;  // K-blocks of B (hi and lo) that fit beside the A ring: K <= 128
 
@@ -337,7 +357,7 @@ __global__ void __launch_bounds__(kWsThreads, 1)
 proj_gemm_ws_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_constant__ CUtensorMap mapB1hi,
                     const __grid_constant__ CUtensorMap mapB1lo, const __grid_constant__ CUtensorMap mapA2,
                     const __grid_constant__ CUtensorMap mapB2hi, const __grid_constant__ CUtensorMap mapB2lo,
-                    const ProjArgs p) {
+                    const __grid_constant__ CUtensorMap mapC, const ProjArgs p) {
     extern __shared__ unsigned char smem_raw[];
     __shared__ __align__(8) WsBars bars;
     __shared__ uint32_t tmem_base_slot;
@@ -513,8 +533,8 @@ proj_gemm_ws_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_cons
         }
     } else {
         // ------------------------------------------------------------ epilogue (warps 0-3)
-        float* patch = patches + wid * (32 * 36);
-        long long ti = 0;
+        float* patch = patches + wid * (2 * 32 * 32);  // this warp's two patches (the plain path uses them as one, pitch 36)
+        long long ti = 0, pc = 0;                        // tiles and patches done
         for (long long t = t_begin; t < t_end && !abort_flag; t += t_step, ++ti) {
             long long m_tile, n_tile;
             decode(t, m_tile, n_tile);
@@ -531,6 +551,31 @@ proj_gemm_ws_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_cons
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&bars.acc_empty[buf])) : "memory");
                 }
+                const long long gc0 = col0 + c * 32;
+                if (p.tma_c) {
+                    if (gc0 >= p.N) continue;  // a column chunk past the end (uniform over the warp)
+                    if (p.bias != nullptr) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (gc0 + j < p.N) v[j] += __ldg(p.bias + gc0 + j);
+                    }
+                    float* pt = patch + (int)(pc & 1) * (32 * 32);
+                    if (lane == 0) bulk_wait_read<1>();  // the store that read this patch two patches ago is done with it
+                    __syncwarp();
+                    // row `lane` of the patch: its q-th 16-byte piece sits at piece q ^ (lane % 8)
+#pragma unroll
+                    for (int q = 0; q < 8; ++q)
+                        *reinterpret_cast<float4*>(pt + lane * 32 + ((q ^ (lane & 7)) << 2)) =
+                            make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> visible to the TMA unit
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_2d(&mapC, pt, (int)gc0, (int)(row0 + wid * 32));
+                        bulk_commit();
+                    }
+                    ++pc;  // one group per patch: the patches alternate exactly with the groups
+                    continue;
+                }
 #pragma unroll
                 for (int q = 0; q < 8; ++q)
                     *reinterpret_cast<float4*>(patch + lane * 36 + q * 4) = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
@@ -539,7 +584,7 @@ proj_gemm_ws_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_cons
 #pragma unroll
                 for (int rr = 0; rr < 8; ++rr) {
                     const int r = rr * 4 + (lane >> 3);
-                    const long long grow = row0 + wid * 32 + r, gcol = col0 + c * 32 + cc;
+                    const long long grow = row0 + wid * 32 + r, gcol = gc0 + cc;
                     if (grow < p.M && gcol < p.N) {
                         float4 o = *reinterpret_cast<const float4*>(patch + r * 36 + cc);
                         if (p.bias != nullptr) {
@@ -560,6 +605,7 @@ proj_gemm_ws_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_cons
                 __syncwarp();
             }
         }
+        if (lane == 0) bulk_wait_all();  // this warp's stores have left shared memory and are complete
     }
     __syncwarp();  // the single-lane roles rejoin their warps before the CTA-wide barrier below
     // wind down together; copies a producer has in flight get a bounded time to land before the CTA's
@@ -900,6 +946,9 @@ int b200_proj_gemm(int64_t M, int64_t N, int64_t K1, const void* A1, int64_t lda
     }
     ProjArgs a;
     a.C = (float*)C, a.bias = (const float*)bias, a.ldc = ldc, a.M = M, a.N = N;
+    // C through TMA when its rows are 16-byte aligned (32 x 32 boxes, 128-byte swizzle in shared memory)
+    CUtensorMap mC = mA1;
+    a.tma_c = (PROJ_TMA_STORE && row_ok(C, ldc) && make_map(&mC, (const float*)C, M, N, ldc, 32)) ? 1 : 0;
     a.kb1 = (int)((K1 + kBK - 1) / kBK), a.kb2 = (int)((K2 + kBK - 1) / kBK);  // a ragged last block reads zeros past K
     a.hdr = reinterpret_cast<WsHeader*>(base);
 #ifdef PROJ_GEMM_SIMPLE
@@ -912,9 +961,9 @@ int b200_proj_gemm(int64_t M, int64_t N, int64_t K1, const void* A1, int64_t lda
     } else if (PROJ_RESIDENT && a.kb2 == 0 && a.kb1 <= kResidentKb && n_tiles <= sms) {
         // short K: the column tile's weights stay in shared memory; whole groups of n_tiles CTAs
         const long long grid = sms - sms % n_tiles;
-        proj_gemm_ws_kernel<true><<<(unsigned int)grid, kWsThreads, kWsSmem, st>>>(mA1, mB1h, mB1l, mA2, mB2h, mB2l, a);
+        proj_gemm_ws_kernel<true><<<(unsigned int)grid, kWsThreads, kWsSmem, st>>>(mA1, mB1h, mB1l, mA2, mB2h, mB2l, mC, a);
     } else {
-        proj_gemm_ws_kernel<false><<<(unsigned int)sms, kWsThreads, kWsSmem, st>>>(mA1, mB1h, mB1l, mA2, mB2h, mB2l, a);
+        proj_gemm_ws_kernel<false><<<(unsigned int)sms, kWsThreads, kWsSmem, st>>>(mA1, mB1h, mB1l, mA2, mB2h, mB2l, mC, a);
     }
 #endif
     return cudaGetLastError() == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
