@@ -341,7 +341,8 @@ def run_gpu(args):
     if not args.kernel_only:
         timed = _make_timed(torch, dev)
         for name in ("C1", "C3", "C4"):
-            others[name] = _kernel_only(name, torch, dev, rank, timed, max(10, min(args.steps, 20)))
+            others[name] = _kernel_only(name, torch, dev, rank, timed, max(10, min(args.steps, 20)),
+                                        with_cpu=world == 1 and rank == 0 and not args.no_cpu)
             torch.cuda.empty_cache()
         try:
             c5 = _c5_measure(torch, dist, dev, world, rank, local, barrier, steps=max(5, min(args.steps, 10)), warmup=3)
@@ -453,8 +454,26 @@ def _e2e(args, torch, tsfast_b200, dev, a, b, g, barrier):
                 "pinned_host_bytes": 6 * E2E_STREAMS * rows * T * D * 4}
 
 
-def _kernel_only(name, torch, dev, rank, timed, steps):
-    """Forward and adjoint kernels of one of the other configurations, device-resident, event-timed."""
+def _reference_cpu_leg(wl, torch, seconds_target: float = 3.0):
+    """The reference's own CPU implementation of a workload (its `ref_cpu` closure) on a few batch
+    rows, scaled to the whole batch; None with the reason when that path cannot run here."""
+    try:
+        rows = wl.get("ref_rows", wl["sample_rows"])
+        torch.set_num_threads(_host_threads())
+        one, what = wl["ref_cpu"](rows)
+        one()  # compiles the reference's C/C++ kernel on first use
+        sec, cnt = _time_cpu(one, 1, 1, seconds_target)
+        step_bytes = wl["fwd_bytes"] + wl["bwd_bytes"]
+        return {"value": round(step_bytes * rows / wl["rows"] / sec / 1e9, 3), "unit": "GB/s", "cores": torch.get_num_threads(),
+                "kind": "reference", "sample": f"{rows} of {wl['rows']} batch rows, fwd+bwd on fresh leaves, median of {cnt} "
+                                               f"passes of {sec * 1e3:.1f} ms; {what}"}, None
+    except Exception as e:
+        return None, f"the reference's own path was not usable: {type(e).__name__}: {str(e)[:120]}"
+
+
+def _kernel_only(name, torch, dev, rank, timed, steps, with_cpu=False):
+    """Forward and adjoint kernels of one of the other configurations, device-resident, event-timed
+    (with_cpu: the reference's CPU path for the same workload timed beside them)."""
     wl = _workload(name, torch, dev, rank, host_buffers=False)
     keep = {}
 
@@ -470,11 +489,15 @@ def _kernel_only(name, torch, dev, rank, timed, steps):
     bwd_ms = timed(lambda: wl["bwd"](keep["o"]), steps)
     peak, _ = _peaks()
     step_bytes = wl["fwd_bytes"] + wl["bwd_bytes"]
-    return {"workload": wl["desc"], "gbs": round(step_bytes / ms / 1e6, 1), "ms_per_step": round(ms, 4), "steps": steps,
-            "fwd_ms": round(fwd_ms, 4), "bwd_ms": round(bwd_ms, 4),
-            "fwd_frac": round(wl["fwd_bytes"] / fwd_ms / 1e6 / peak, 4), "bwd_frac": round(wl["bwd_bytes"] / bwd_ms / 1e6 / peak, 4),
-            "algorithmic_bytes_per_step": step_bytes, "traffic": wl.get("traffic"),
-            "state_elements_per_s": round(wl["elems"] / (ms * 1e-3))}
+    rec = {"workload": wl["desc"], "gbs": round(step_bytes / ms / 1e6, 1), "ms_per_step": round(ms, 4), "steps": steps,
+           "fwd_ms": round(fwd_ms, 4), "bwd_ms": round(bwd_ms, 4),
+           "fwd_frac": round(wl["fwd_bytes"] / fwd_ms / 1e6 / peak, 4), "bwd_frac": round(wl["bwd_bytes"] / bwd_ms / 1e6 / peak, 4),
+           "algorithmic_bytes_per_step": step_bytes, "traffic": wl.get("traffic"),
+           "state_elements_per_s": round(wl["elems"] / (ms * 1e-3))}
+    if with_cpu and "ref_cpu" in wl:
+        base, why = _reference_cpu_leg(wl, torch)
+        rec["cpu_baseline"] = base if base is not None else {"unavailable": why}
+    return rec
 
 
 def _triton_baseline(torch, dev, timed):
@@ -614,7 +637,17 @@ def _workload(name, torch, dev, rank, host_buffers=True, impl="b200"):
             a_, v_, g_, x_ = (t[:rows].cpu().numpy() for t in (lam, v, g, x0))
             return lambda: O.diag_bwd(g_, a_, O.diag_fwd(a_, v_, x_), x_)
 
-        return dict(desc="C1: complex LRU diagonal scan fwd+bwd, B=16 T=1000 D=64 complex64, carry-in x0",
+        def ref_cpu(rows):  # tsfast's generated-C++ diagonal kernel (scan_backends/diagonal_c.py) through its public function
+            ref_scan, use_backend = _import_reference()
+            l_, v_, g_, x_ = lam1.cpu(), v[:rows].cpu(), g[:rows].cpu(), x0[:rows].cpu()
+
+            def one():
+                lq, vq, xq = l_.clone().requires_grad_(), v_.clone().requires_grad_(), x_.clone().requires_grad_()
+                with use_backend("c"):
+                    ref_scan.diagonal_recurrence(lq, vq, xq).backward(g_)
+            return one, "diagonal_recurrence under use_backend('c') (tsfast's generated-C++ diagonal_c kernel)"
+
+        return dict(desc="C1: complex LRU diagonal scan fwd+bwd, B=16 T=1000 D=64 complex64, carry-in x0", ref_cpu=ref_cpu,
                     fwd_bytes=2 * E, bwd_bytes=3 * E, elems=2 * M * L * N, rows=M, sample_rows=M, flush=True,
                     h2d=3 * E, d2h=2 * E, dtype="c64", launches=2, kernel="diag_scan_kernel<float2, const, adjoint> (b200_diag_bwd)",
                     fwd=lambda: diagonal_b200.forward(lam, v, x0), bwd=lambda o: diagonal_b200.backward(g, lam, o, x0),
@@ -646,8 +679,24 @@ def _workload(name, torch, dev, rank, host_buffers=True, impl="b200"):
             go = gout[:rows].cpu().numpy()
             return lambda: (O.mamba_fwd(*a), O.mamba_bwd(*a, go, None))
 
+        def ref_cpu(rows):  # tsfast's C kernel for the fused section (architectures/mamba/backend_c.py)
+            _import_reference()
+            from tsfast.models.architectures.mamba import backend_c
+
+            host = [None if t is None else (t[:rows].cpu() if t.dim() == 3 else t.cpu()) for t in ins]
+            go = gout[:rows].cpu()
+            why = backend_c.supports(*host)
+            if why is not None:
+                raise RuntimeError(why)
+
+            def one():
+                leaves = [None if t is None else t.clone().requires_grad_() for t in host]
+                out, _ = backend_c.run(*leaves)
+                out.backward(go)
+            return one, "mamba.backend_c.run (tsfast's C kernel for the fused selective-scan section)"
+
         return dict(desc="C3: Mamba selective scan fwd+bwd, B=32 T=2048 D_inner=512 N=16 fp32, S4D-real A, D=1, SiLU gate",
-                    fwd_bytes=4 * big + 2 * small + Bn * D * N * 4, bwd_bytes=7 * big + 4 * small,
+                    ref_cpu=ref_cpu, fwd_bytes=4 * big + 2 * small + Bn * D * N * 4, bwd_bytes=7 * big + 4 * small,
                     elems=2 * Bn * L * D * N, rows=Bn, sample_rows=2, flush=False, h2d=4 * big + 2 * small + big,
                     d2h=4 * big + 2 * small, dtype="f32", launches=6, kernel="mamba_bwd_kernel<TPC=4> (b200_mamba_bwd)",
                     traffic=815_733_248 + 499_814_144,  # ncu dram__bytes read + write of one adjoint launch at this shape
@@ -683,8 +732,24 @@ def _workload(name, torch, dev, rank, host_buffers=True, impl="b200"):
             a_, w_, g_ = a[: rows * P].cpu().numpy(), w[: rows * P].cpu().numpy(), g[: rows * P].cpu().numpy()
             return lambda: O.allpole_bwd(g_, a_, O.allpole_fwd(a_, w_, None), None)
 
-        return dict(desc="C4: dynoNet all-pole IIR scan fwd+bwd, B=128 x 128 channels, T=8192 fp32, order 4",
-                    fwd_bytes=2 * E, bwd_bytes=3 * E, elems=2 * Bn * P * L, rows=Bn, sample_rows=8, flush=False,
+        def ref_cpu(rows):  # tsfast's only CPU path for the all-pole filter: the companion-matrix doubling scan
+            _import_reference()
+            import torch.nn.functional as F
+            from tsfast.models.architectures.dynonet.core import linear_recurrence
+
+            ac = a_p.cpu()
+            shift = torch.eye(4)[:-1].expand(P, 3, 4)
+            w_, g_ = w[: rows * P].cpu().view(rows, P, L), g[: rows * P].cpu().view(rows, P, L)
+
+            def one():
+                aq, wq = ac.clone().requires_grad_(), w_.clone().requires_grad_()
+                comp = torch.cat((-aq.unsqueeze(1), shift), dim=1)  # dynonet/core.py:186-190
+                x = linear_recurrence(comp, F.pad(wq.unsqueeze(-1), (0, 3)), None)
+                x[..., 0].backward(g_)
+            return one, "linear_recurrence over the companion form (dynonet/core.py:103-141, 231), tsfast's CPU path for S4"
+
+        return dict(desc="C4: dynoNet all-pole IIR scan fwd+bwd, B=128 x 128 channels, T=8192 fp32, order 4", ref_cpu=ref_cpu,
+                    ref_rows=1, fwd_bytes=2 * E, bwd_bytes=3 * E, elems=2 * Bn * P * L, rows=Bn, sample_rows=8, flush=False,
                     h2d=2 * E, d2h=2 * E, dtype="f32", launches=2, kernel="allpole_kernel<NA=4, adjoint> (b200_allpole_bwd)",
                     traffic=1_074_100_000 + 501_500_000,  # ncu dram__bytes read + write of one adjoint launch at this shape
                     fwd=lambda: allpole_b200._allpole_op(a, w, None), bwd=lambda o: allpole_b200._allpole_bwd_op(g, a, o, None),
@@ -877,11 +942,15 @@ def run_workload(args):
             from oracle import oracle as O
             O.build()
             O.set_num_threads(_host_threads())
-            rows = wl["sample_rows"]
-            sec, cnt = _time_cpu(wl["cpu"](rows), 1, 1, 10.0)
-            base = {"value": round(step_bytes * rows / wl["rows"] / sec / 1e9, 3), "unit": "GB/s", "cores": O.num_threads(),
-                    "kind": "port", "sample": f"{rows} of {wl['rows']} batch rows, fwd+bwd, median of {cnt} passes of "
-                    f"{sec * 1e3:.1f} ms; float32 C port of the reference's CPU algorithm, OpenMP"}
+            base, why = None, "no reference leg for this workload"
+            if "ref_cpu" in wl:  # the reference's own CPU implementation, from the copy under oracle/_ref
+                base, why = _reference_cpu_leg(wl, torch, 10.0)
+            if base is None:
+                rows = wl["sample_rows"]
+                sec, cnt = _time_cpu(wl["cpu"](rows), 1, 1, 10.0)
+                base = {"value": round(step_bytes * rows / wl["rows"] / sec / 1e9, 3), "unit": "GB/s", "cores": O.num_threads(),
+                        "kind": "port", "sample": f"{rows} of {wl['rows']} batch rows, fwd+bwd, median of {cnt} passes of "
+                        f"{sec * 1e3:.1f} ms; float32 C port of the reference's CPU algorithm, OpenMP ({why})"}
         bwd_gbs, fwd_gbs = wl["bwd_bytes"] / bwd_ms / 1e6, wl["fwd_bytes"] / fwd_ms / 1e6
         extra = wl["extra"](timed) if "extra" in wl else {}
         _emit({
