@@ -126,7 +126,7 @@ def test_projections_on_tensor_cores_match_float64_reference(tsfast_installed, f
     m = tsfast_installed
     import tsfast_b200
     from tsfast.models import use_backend
-    from tsfast_b200 import proj_b200
+    from tsfast_b200 import prologue_b200, proj_b200
 
     torch.manual_seed(0)
     if family == "lru":
@@ -141,13 +141,15 @@ def test_projections_on_tensor_cores_match_float64_reference(tsfast_installed, f
     tsfast_b200.install(fuse_projections=True)
     n_lin = tsfast_b200.accelerate_linears(model32)
     assert n_lin >= 2
-    before = proj_b200.calls
+    before, before_prologue = proj_b200.calls, prologue_b200.calls
     try:
         with use_backend("auto"):
             got = _chunked(model32, u, (90,))
             (got**2).mean().backward()
         used = proj_b200.calls - before
         assert used >= 6 * n_lin // 2, f"only {used} launches of the projection kernels"
+        if family in ("lru", "s5"):  # eigenvalues / discretisation: one launch forward and one backward per layer and chunk
+            assert prologue_b200.calls - before_prologue >= 2 * 2, "the parameter prologue kernels did not run"
         with use_backend("reference"):
             want = _chunked(model64, u.double(), (90,))
             (want**2).mean().backward()
