@@ -781,6 +781,212 @@ proj_wgrad_kernel(const __grid_constant__ CUtensorMap mapG, const __grid_constan
     }
 }
 
+// ------------------------------------------------------------------------------ pipelined weight gradient
+// The same tile of dW = G^T A with the phases of consecutive token blocks overlapped and the G operand
+// in tensor memory.  160 threads: warps 0-3 split, lane 0 of warp 4 asks for the copies and issues the
+// MMAs.  Per stage (two of them): the TMA unit brings the raw G block [32 tokens x 128 columns]
+// (unswizzled: thread f reads column f down the tokens, conflict-free) and the A block (token-major,
+// 32-byte-atom swizzle, as above); the splitters write G's hi and lo halves into tensor memory - feature
+// f is lane f, the 32 tokens are 32 columns - from where the MMAs take them as their A operand, and
+// split the A block in place (hi) and beside it (lo); the issuer launches the 12 MMAs (A from tensor
+// memory, B = the activations, MN-major from shared memory), waits for them and asks for the block after
+// next into the same stage while the splitters are busy with the other stage.  G never goes back to
+// shared memory and is never read from there by the tensor core: a third less shared-memory traffic
+// per block than proj_wgrad_kernel, and no full stop between copy, split and MMA.
+constexpr int kWgStages = 2;
+constexpr int kWgStageBytes = 3 * kTileBytes;  // raw G, A (hi in place), A lo
+constexpr int kWgSmem = kWgStages * kWgStageBytes + 1024;
+constexpr int kWgThreads = 160;
+constexpr uint32_t kIdescTsMN = kIdesc | (1u << 16);  // A from tensor memory, B MN-major
+
+__device__ __forceinline__ void umma_tf32_ts_mn(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "r"(tmem_a), "l"(bdesc), "r"(kIdescTsMN), "r"(accumulate)
+        : "memory");
+}
+
+__global__ void __launch_bounds__(kWgThreads, 2)
+proj_wgrad_ws_kernel(const __grid_constant__ CUtensorMap mapGraw, const __grid_constant__ CUtensorMap mapA, const WgradArgs p) {
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ __align__(8) uint64_t full[kWgStages], ready[kWgStages], done[kWgStages];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ volatile int abort_flag;
+    const int tid = threadIdx.x, wid = tid >> 5, lane = tid & 31;
+    unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    auto sG = [&](int s) { return reinterpret_cast<float*>(base + s * kWgStageBytes); };
+    auto sA = [&](int s) { return reinterpret_cast<float*>(base + s * kWgStageBytes + kTileBytes); };
+    auto sAlo = [&](int s) { return reinterpret_cast<float*>(base + s * kWgStageBytes + 2 * kTileBytes); };
+
+    const int tiles = p.n_tiles * p.k_tiles;
+    const int split = blockIdx.x / tiles, t = blockIdx.x - split * tiles;
+    const int n_tile = t / p.k_tiles, k_tile = t - n_tile * p.k_tiles;
+    const int n0 = n_tile * 128, k0 = k_tile * 128;
+    const long long tok0 = (long long)split * p.tok_per_split;
+    long long tok1 = tok0 + p.tok_per_split;
+    if (tok1 > p.M) tok1 = p.M;
+    const int nblk = tok1 > tok0 ? (int)((tok1 - tok0 + kTok - 1) / kTok) : 0;
+
+    if (tid == 0) {
+        for (int s = 0; s < kWgStages; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&ready[s], 128);
+            mbar_init(&done[s], 1);
+        }
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (wid == 4) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(256)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_d = tmem_base_slot;          // accumulator: columns [0, 128)
+    const uint32_t tmem_g = tmem_d + 128u;           // G operand: stage s at columns 128 + 64 s (hi) and + 32 (lo)
+
+    auto wait = [&](uint64_t* bar, uint32_t parity) -> bool {
+        const uint32_t a = smem_u32(bar);
+        for (int i = 0; i < kWaitLimit; ++i) {
+            uint32_t ok;
+            asm volatile(
+                "{\n\t.reg .pred p;\n\t"
+                "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                "selp.u32 %0, 1, 0, p;\n\t}"
+                : "=r"(ok)
+                : "r"(a), "r"(parity)
+                : "memory");
+            if (ok) return true;
+            if (abort_flag) return false;
+            __nanosleep(32);
+        }
+        abort_flag = 1;
+        return false;
+    };
+
+    if (wid == 4) {
+        // ------------------------------------------------------------ copies and MMAs (one lane)
+        if (lane == 0) {
+            // rows past the slice's end but inside M belong to the next slice: slices are whole multiples of
+            // kTok, so only the last one meets the end of the matrix (where the tensor maps fill zeros)
+            auto request = [&](int kb) {
+                const int s = kb % kWgStages;
+                const int row = (int)(tok0 + (long long)kb * kTok);
+                mbar_expect_tx(&full[s], 2 * kTileBytes);
+                tma_load_2d(sG(s), &mapGraw, n0, row, &full[s]);
+#pragma unroll
+                for (int cb = 0; cb < 4; ++cb)
+                    tma_load_2d(reinterpret_cast<unsigned char*>(sA(s)) + cb * kColBlk, &mapA, k0 + cb * 32, row, &full[s]);
+            };
+            for (int kb = 0; kb < kWgStages && kb < nblk; ++kb) request(kb);
+            for (int kb = 0; kb < nblk && !abort_flag; ++kb) {
+                const int s = kb % kWgStages;
+                const uint32_t ph = (uint32_t)((kb / kWgStages) & 1);
+                if (!wait(&ready[s], ph)) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t gHi = tmem_g + (uint32_t)(s * 64), gLo = gHi + 32u;
+                const uint64_t dA = umma_desc_mn_sw128(smem_u32(sA(s))), dAl = umma_desc_mn_sw128(smem_u32(sAlo(s)));
+#pragma unroll
+                for (int g = 0; g < kTok / 8; ++g) {  // 8 tokens per MMA: 8 columns of G, the next 1024-byte group of A
+                    const uint64_t adv = (uint64_t)(g * (1024 >> 4));
+                    umma_tf32_ts_mn(tmem_d, gLo + (uint32_t)(8 * g), dA + adv, (kb | g) != 0);
+                    umma_tf32_ts_mn(tmem_d, gHi + (uint32_t)(8 * g), dAl + adv, 1u);
+                    umma_tf32_ts_mn(tmem_d, gHi + (uint32_t)(8 * g), dA + adv, 1u);
+                }
+                umma_commit(&done[s]);
+                // the stage (shared and tensor memory) is free once these MMAs have read it; the other stage
+                // is being split meanwhile
+                if (kb + kWgStages < nblk) {
+                    if (!wait(&done[s], ph)) break;
+                    request(kb + kWgStages);
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ splitters (warps 0-3), then the epilogue
+        const uint32_t lane_field = (uint32_t)(wid * 32) << 16;
+        bool fine = true;
+        for (int kb = 0; kb < nblk && !abort_flag; ++kb) {
+            const int s = kb % kWgStages;
+            if (!wait(&full[s], (uint32_t)((kb / kWgStages) & 1))) {
+                fine = false;
+                break;
+            }
+            // G: column tid of the block, token by token -> lane tid of tensor memory, 32 columns hi, 32 lo
+            const float* gcol = sG(s) + tid;
+            const uint32_t dst = tmem_g + lane_field + (uint32_t)(s * 64);
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                float hi[16], lo[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) split_tf32(gcol[(half * 16 + j) * 128], hi[j], lo[j]);
+                tmem_st16(dst + (uint32_t)(half * 16), hi);
+                tmem_st16(dst + 32u + (uint32_t)(half * 16), lo);
+            }
+            // A: hi in place, lo beside it (same swizzled position)
+            float4* a4 = reinterpret_cast<float4*>(sA(s));
+            float4* l4 = reinterpret_cast<float4*>(sAlo(s));
+#pragma unroll
+            for (int j = 0; j < kTileBytes / 16 / 128; ++j) {
+                const float4 y = a4[j * 128 + tid];
+                float4 h, l;
+                split_tf32(y.x, h.x, l.x), split_tf32(y.y, h.y, l.y), split_tf32(y.z, h.z, l.z), split_tf32(y.w, h.w, l.w);
+                a4[j * 128 + tid] = h;
+                l4[j * 128 + tid] = l;
+            }
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the tensor core
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&ready[s])) : "memory");
+        }
+        // all MMAs have finished once the last block's have (they complete in order)
+        if (fine && nblk > 0 && !wait(&done[(nblk - 1) % kWgStages], (uint32_t)(((nblk - 1) / kWgStages) & 1))) fine = false;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (fine && !abort_flag) {
+            // accumulator lane = row of dW (column of G), accumulator column = column of dW (column of A)
+            float* patch = reinterpret_cast<float*>(base) + wid * (32 * 36);
+            float* dst_tile = p.part + (long long)split * p.N * p.Kp;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                float v[32];
+                if (nblk > 0) {
+                    tmem_ld32(tmem_d + lane_field + (uint32_t)(c * 32), v);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = 0.f;
+                }
+#pragma unroll
+                for (int q = 0; q < 8; ++q)
+                    *reinterpret_cast<float4*>(patch + lane * 36 + q * 4) = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                __syncwarp();
+                const int cc = (lane & 7) * 4;
+#pragma unroll
+                for (int rr = 0; rr < 8; ++rr) {
+                    const int r = rr * 4 + (lane >> 3);
+                    const long long grow = (long long)n0 + wid * 32 + r, gcol2 = (long long)k0 + c * 32 + cc;
+                    if (grow < p.N && gcol2 < p.Kp)  // Kp is a multiple of 4: whole float4 pieces
+                        *reinterpret_cast<float4*>(dst_tile + grow * p.Kp + gcol2) = *reinterpret_cast<const float4*>(patch + r * 36 + cc);
+                }
+                __syncwarp();
+            }
+        }
+    }
+    __syncwarp();
+    if (abort_flag && tid == 0) {
+        atomicExch(&p.hdr->error, (unsigned int)B200_ERR_TIMEOUT);
+        for (int i = 0; i < 1000; ++i) __nanosleep(1000);  // give copies still in flight a bounded time to land
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (wid == 4) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(256) : "memory");
+    }
+}
+
 // dW[n][k] = sum over slices of part[s][n][k] in a fixed order (reproducible)
 __global__ void wgrad_reduce_kernel(const float* __restrict__ part, int splits, long long N, long long K, long long Kp,
                                     float* __restrict__ dW, long long lddw) {
@@ -822,14 +1028,15 @@ static EncodeTiledFn encode_fn() {
 }
 
 // Tensor map of a row-major float32 matrix [rows, cols] (row pitch ld floats) read in boxes of
-// kBK columns x box_rows rows into the 128-byte-swizzled layout; rows and columns past the end read as zero.
+// box_cols (kBK unless stated) columns x box_rows rows into the named shared-memory layout; rows and columns
+// past the end read as zero.
 static bool make_map(CUtensorMap* map, const float* ptr, long long rows, long long cols, long long ld, int box_rows = kBM,
-                     CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
+                     CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B, int box_cols = kBK) {
     EncodeTiledFn fn = encode_fn();
     if (fn == nullptr) return false;
     const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
     const cuuint64_t strides[1] = {(cuuint64_t)ld * sizeof(float)};
-    const cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)box_rows};
+    const cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
     const cuuint32_t estr[2] = {1, 1};
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(ptr), dims, strides, box, estr,
               CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
@@ -853,7 +1060,12 @@ static ProjWs proj_ws(long long N, long long K1, long long K2) {
 }
 
 
-// Token slices of the weight gradient: enough CTAs for about three per SM, slices a multiple of kTok.
+// Token slices of the weight gradient: enough CTAs to fill every SM (two of the pipelined kernel, which
+// tensor memory bounds, three of the plain one), slices a multiple of kTok.
+#ifndef PROJ_WGRAD_WS
+#define PROJ_WGRAD_WS 1
+#endif
+constexpr int kWgradCtasPerSm = PROJ_WGRAD_WS ? 2 : 3;
 struct WgradPlan {
     int n_tiles, k_tiles, splits;
     long long tok_per_split, Kp;
@@ -864,7 +1076,7 @@ static WgradPlan wgrad_plan(long long M, long long N, long long K) {
     w.n_tiles = (int)((N + 127) / 128), w.k_tiles = (int)((K + 127) / 128);
     w.Kp = pad4(K);
     const long long tiles = (long long)w.n_tiles * w.k_tiles;
-    long long want = (3 * 148 + tiles - 1) / tiles;  // slices so that every SM has about three CTAs
+    long long want = (kWgradCtasPerSm * 148 + tiles - 1) / tiles;  // slices so that every SM has its resident CTAs
     const long long blocks = (M + kTok - 1) / kTok;
     if (want > blocks) want = blocks;
     if (want < 1) want = 1;
@@ -989,15 +1201,17 @@ int b200_proj_wgrad(int64_t M, int64_t N, int64_t K, const void* G, int64_t ldg,
     char* base = static_cast<char*>(workspace);
     if (cudaMemsetAsync(base, 0, sizeof(WsHeader), st) != cudaSuccess) return B200_ERR_LAUNCH;
     CUtensorMap mG, mA;
-    // token-major operands of 4-byte elements use the 128-byte swizzle whose unit is a 32-byte chunk
-    if (!make_map(&mG, (const float*)G, M, N, ldg, kTok, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B) ||
-        !make_map(&mA, (const float*)A, M, K, lda, kTok, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B))
-        return B200_ERR_LAUNCH;
+    // token-major operands of 4-byte elements use the 128-byte swizzle whose unit is a 32-byte chunk; the
+    // pipelined kernel takes G as plain rows of 128 columns (its threads read it, not the tensor core)
+    const bool g_ok = PROJ_WGRAD_WS ? make_map(&mG, (const float*)G, M, N, ldg, kTok, CU_TENSOR_MAP_SWIZZLE_NONE, 128)
+                                    : make_map(&mG, (const float*)G, M, N, ldg, kTok, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
+    if (!g_ok || !make_map(&mA, (const float*)A, M, K, lda, kTok, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) return B200_ERR_LAUNCH;
     static bool configured[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !configured[dev]) {
-        if (cudaFuncSetAttribute(proj_wgrad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem) != cudaSuccess)
+        if (cudaFuncSetAttribute(proj_wgrad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem) != cudaSuccess ||
+            cudaFuncSetAttribute(proj_wgrad_ws_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kWgSmem) != cudaSuccess)
             return B200_ERR_LAUNCH;
         configured[dev] = true;
     }
@@ -1008,7 +1222,10 @@ int b200_proj_wgrad(int64_t M, int64_t N, int64_t K, const void* G, int64_t ldg,
     a.hdr = reinterpret_cast<WsHeader*>(base);
     const long long grid = (long long)w.splits * w.n_tiles * w.k_tiles;
     if (grid > 0x7fffffffLL) return B200_ERR_UNSUPPORTED;
-    proj_wgrad_kernel<<<(unsigned int)grid, 128, kGemmSmem, st>>>(mG, mA, a);
+    if (PROJ_WGRAD_WS)
+        proj_wgrad_ws_kernel<<<(unsigned int)grid, kWgThreads, kWgSmem, st>>>(mG, mA, a);
+    else
+        proj_wgrad_kernel<<<(unsigned int)grid, 128, kGemmSmem, st>>>(mG, mA, a);
     if (cudaGetLastError() != cudaSuccess) return B200_ERR_LAUNCH;
     wgrad_reduce_kernel<<<(unsigned int)((N * K + 255) / 256), 256, 0, st>>>(a.part, w.splits, N, K, w.Kp, (float*)dW, lddw);
     return cudaGetLastError() == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
