@@ -783,8 +783,8 @@ proj_wgrad_kernel(const __grid_constant__ CUtensorMap mapG, const __grid_constan
 
 // ------------------------------------------------------------------------------ pipelined weight gradient
 // The same tile of dW = G^T A with the phases of consecutive token blocks overlapped and the G operand
-// in tensor memory.  160 threads: warps 0-3 split, lane 0 of warp 4 asks for the copies and issues the
-// MMAs.  Per stage (two of them): the TMA unit brings the raw G block [32 tokens x 128 columns]
+// in tensor memory.  288 threads: warps 0-3 split G, warps 4-7 split A, lane 0 of warp 8 asks for the
+// copies and issues the MMAs.  Per stage (two of them): the TMA unit brings the raw G block [32 tokens x 128 columns]
 // (unswizzled: thread f reads column f down the tokens, conflict-free) and the A block (token-major,
 // 32-byte-atom swizzle, as above); the splitters write G's hi and lo halves into tensor memory - feature
 // f is lane f, the 32 tokens are 32 columns - from where the MMAs take them as their A operand, and
@@ -796,7 +796,7 @@ proj_wgrad_kernel(const __grid_constant__ CUtensorMap mapG, const __grid_constan
 constexpr int kWgStages = 2;
 constexpr int kWgStageBytes = 3 * kTileBytes;  // raw G, A (hi in place), A lo
 constexpr int kWgSmem = kWgStages * kWgStageBytes + 1024;
-constexpr int kWgThreads = 160;
+constexpr int kWgThreads = 288;  // warps 0-3 split G, warps 4-7 split A, warp 8 copies and issues
 constexpr uint32_t kIdescTsMN = kIdesc | (1u << 16);  // A from tensor memory, B MN-major
 
 __device__ __forceinline__ void umma_tf32_ts_mn(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t accumulate) {
@@ -832,13 +832,13 @@ proj_wgrad_ws_kernel(const __grid_constant__ CUtensorMap mapGraw, const __grid_c
     if (tid == 0) {
         for (int s = 0; s < kWgStages; ++s) {
             mbar_init(&full[s], 1);
-            mbar_init(&ready[s], 128);
+            mbar_init(&ready[s], 256);
             mbar_init(&done[s], 1);
         }
         abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (wid == 4) {
+    if (wid == 8) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(256)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -868,7 +868,7 @@ proj_wgrad_ws_kernel(const __grid_constant__ CUtensorMap mapGraw, const __grid_c
         return false;
     };
 
-    if (wid == 4) {
+    if (wid == 8) {
         // ------------------------------------------------------------ copies and MMAs (one lane)
         if (lane == 0) {
             // rows past the slice's end but inside M belong to the next slice: slices are whole multiples of
@@ -907,8 +907,10 @@ proj_wgrad_ws_kernel(const __grid_constant__ CUtensorMap mapGraw, const __grid_c
             }
         }
     } else {
-        // ------------------------------------------------------------ splitters (warps 0-3), then the epilogue
-        const uint32_t lane_field = (uint32_t)(wid * 32) << 16;
+        // ------------------------------------------------------------ splitters (warps 0-3: G, 4-7: A); warps 0-3 then the epilogue
+        const uint32_t lane_field = (uint32_t)((wid & 3) * 32) << 16;
+        const bool g_side = wid < 4;
+        const int st = tid & 127;  // index among the 128 threads of this side
         bool fine = true;
         for (int kb = 0; kb < nblk && !abort_flag; ++kb) {
             const int s = kb % kWgStages;
@@ -916,37 +918,40 @@ proj_wgrad_ws_kernel(const __grid_constant__ CUtensorMap mapGraw, const __grid_c
                 fine = false;
                 break;
             }
-            // G: column tid of the block, token by token -> lane tid of tensor memory, 32 columns hi, 32 lo
-            const float* gcol = sG(s) + tid;
-            const uint32_t dst = tmem_g + lane_field + (uint32_t)(s * 64);
+            if (g_side) {
+                // G: column st of the block, token by token -> lane st of tensor memory, 32 columns hi, 32 lo
+                const float* gcol = sG(s) + st;
+                const uint32_t dst = tmem_g + lane_field + (uint32_t)(s * 64);
 #pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                float hi[16], lo[16];
+                for (int half = 0; half < 2; ++half) {
+                    float hi[16], lo[16];
 #pragma unroll
-                for (int j = 0; j < 16; ++j) split_tf32(gcol[(half * 16 + j) * 128], hi[j], lo[j]);
-                tmem_st16(dst + (uint32_t)(half * 16), hi);
-                tmem_st16(dst + 32u + (uint32_t)(half * 16), lo);
+                    for (int j = 0; j < 16; ++j) split_tf32(gcol[(half * 16 + j) * 128], hi[j], lo[j]);
+                    tmem_st16(dst + (uint32_t)(half * 16), hi);
+                    tmem_st16(dst + 32u + (uint32_t)(half * 16), lo);
+                }
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            } else {
+                // A: hi in place, lo beside it (same swizzled position)
+                float4* a4 = reinterpret_cast<float4*>(sA(s));
+                float4* l4 = reinterpret_cast<float4*>(sAlo(s));
+#pragma unroll
+                for (int j = 0; j < kTileBytes / 16 / 128; ++j) {
+                    const float4 y = a4[j * 128 + st];
+                    float4 h, l;
+                    split_tf32(y.x, h.x, l.x), split_tf32(y.y, h.y, l.y), split_tf32(y.z, h.z, l.z), split_tf32(y.w, h.w, l.w);
+                    a4[j * 128 + st] = h;
+                    l4[j * 128 + st] = l;
+                }
             }
-            // A: hi in place, lo beside it (same swizzled position)
-            float4* a4 = reinterpret_cast<float4*>(sA(s));
-            float4* l4 = reinterpret_cast<float4*>(sAlo(s));
-#pragma unroll
-            for (int j = 0; j < kTileBytes / 16 / 128; ++j) {
-                const float4 y = a4[j * 128 + tid];
-                float4 h, l;
-                split_tf32(y.x, h.x, l.x), split_tf32(y.y, h.y, l.y), split_tf32(y.z, h.z, l.z), split_tf32(y.w, h.w, l.w);
-                a4[j * 128 + tid] = h;
-                l4[j * 128 + tid] = l;
-            }
-            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the tensor core
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&ready[s])) : "memory");
         }
         // all MMAs have finished once the last block's have (they complete in order)
-        if (fine && nblk > 0 && !wait(&done[(nblk - 1) % kWgStages], (uint32_t)(((nblk - 1) / kWgStages) & 1))) fine = false;
+        if (g_side && fine && nblk > 0 && !wait(&done[(nblk - 1) % kWgStages], (uint32_t)(((nblk - 1) / kWgStages) & 1))) fine = false;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (fine && !abort_flag) {
+        if (g_side && fine && !abort_flag) {
             // accumulator lane = row of dW (column of G), accumulator column = column of dW (column of A)
             float* patch = reinterpret_cast<float*>(base) + wid * (32 * 36);
             float* dst_tile = p.part + (long long)split * p.N * p.Kp;
@@ -982,7 +987,7 @@ proj_wgrad_ws_kernel(const __grid_constant__ CUtensorMap mapGraw, const __grid_c
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (wid == 4) {
+    if (wid == 8) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(256) : "memory");
     }
 }
