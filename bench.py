@@ -827,7 +827,7 @@ def _workload(name, torch, dev, rank, host_buffers=True, impl="b200"):
                          "forward + input gradient + weight gradient",
                     fwd_bytes=big + small, bwd_bytes=2 * (big + small), elems=Mt * N_, rows=128, sample_rows=8, flush=False,
                     h2d=big + small, d2h=big + small, dtype="f32 (tf32 x3)", launches=6,
-                    kernel="proj_gemm_kernel + proj_wgrad_kernel (b200_proj_gemm, b200_proj_wgrad)",
+                    kernel="proj_gemm_ws_kernel + proj_wgrad_ws_kernel (b200_proj_gemm, b200_proj_wgrad)",
                     fwd=lambda: proj_b200._proj_gemm_op(a_, w_, None),
                     bwd=lambda o: (proj_b200._input_grad(g_, w_), proj_b200._proj_wgrad_op(g_, a_)), e2e=e2e, cpu=cpu, extra=extra)
     if name == "G":

@@ -623,16 +623,16 @@ proj_gemm_ws_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_cons
 
 // ================================================================================ weight gradient
 // dW[N, K] = G[M, N]^T * A[M, K]: the reduction runs over the tokens (rows of both operands), which are
-// the slow axis in memory, so both operands reach the tensor core "MN-major": a block of kTok tokens x
-// 32 columns lands as kTok rows of 128 bytes, swizzled in 32-byte chunks with a period of 4 rows (the
-// layout the tensor core expects of MN-major 4-byte elements), and the descriptor names the column
-// axis as the contiguous one (leading byte offset = distance between two 32-column blocks, stride
-// byte offset = 4 tokens = 512 bytes).  An MMA consumes 8 tokens; a CTA owns one
-// 128 x 128 tile of dW for one slice of the token axis, accumulates it in tensor memory over its whole
-// slice and writes it to the workspace; wgrad_reduce_kernel adds the slices in a fixed order.
+// the slow axis in memory.  The activations A reach the tensor core "MN-major" from shared memory: a
+// block of kTok tokens x 32 columns lands as kTok rows of 128 bytes, swizzled in 32-byte chunks with a
+// period of 4 rows (the layout the tensor core expects of MN-major 4-byte elements), and the descriptor
+// names the column axis as the contiguous one (leading byte offset = distance between two 32-column
+// blocks, stride byte offset = 4 tokens = 512 bytes).  The output gradient G goes through tensor memory
+// (below).  An MMA consumes 8 tokens; a CTA owns one 128 x 128 tile of dW for one slice of the token
+// axis, accumulates it in tensor memory over its whole slice and writes it to the workspace;
+// wgrad_reduce_kernel adds the slices in a fixed order.
 constexpr int kTok = 32;                         // tokens per block
 constexpr int kColBlk = kTok * 128;              // bytes of one 32-column block: kTok rows of 128 bytes
-constexpr uint32_t kIdescMN = kIdesc | (1u << 15) | (1u << 16);  // A and B MN-major
 
 __device__ __forceinline__ uint64_t umma_desc_mn_sw128(uint32_t saddr) {
     uint64_t d = (uint64_t)((saddr >> 4) & 0x3FFFu);
@@ -642,15 +642,6 @@ __device__ __forceinline__ uint64_t umma_desc_mn_sw128(uint32_t saddr) {
     d |= (uint64_t)1 << 61;               // 128-byte swizzle with a 32-byte base (4-byte elements, MN-major)
     return d;
 }
-__device__ __forceinline__ void umma_tf32_mn(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
-        "l"(adesc), "l"(bdesc), "r"(kIdescMN), "r"(accumulate)
-        : "memory");
-}
-
 struct WgradArgs {
     float* part;        // [splits][N][Kp] partial sums
     long long M, N, K, Kp;
@@ -659,140 +650,17 @@ struct WgradArgs {
     WsHeader* hdr;
 };
 
-__global__ void __launch_bounds__(128, 3)
-proj_wgrad_kernel(const __grid_constant__ CUtensorMap mapG, const __grid_constant__ CUtensorMap mapA, const WgradArgs p) {
-    extern __shared__ unsigned char smem_raw[];
-    __shared__ __align__(8) uint64_t bar_tma, bar_mma;
-    __shared__ uint32_t tmem_base_slot;
-    const int tid = threadIdx.x, wid = tid >> 5, lane = tid & 31;
-    unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    float* sG = reinterpret_cast<float*>(base);                    // [4 column blocks][kTok][32]
-    float* sGlo = reinterpret_cast<float*>(base + kTileBytes);
-    float* sA = reinterpret_cast<float*>(base + 2 * kTileBytes);
-    float* sAlo = reinterpret_cast<float*>(base + 3 * kTileBytes);
-
-    const int tiles = p.n_tiles * p.k_tiles;
-    const int split = blockIdx.x / tiles, t = blockIdx.x - split * tiles;
-    const int n_tile = t / p.k_tiles, k_tile = t - n_tile * p.k_tiles;
-    const int n0 = n_tile * 128, k0 = k_tile * 128;
-    const long long tok0 = (long long)split * p.tok_per_split;
-    long long tok1 = tok0 + p.tok_per_split;
-    if (tok1 > p.M) tok1 = p.M;
-    const int nblk = tok1 > tok0 ? (int)((tok1 - tok0 + kTok - 1) / kTok) : 0;
-
-    if (tid == 0) {
-        mbar_init(&bar_tma, 1);
-        mbar_init(&bar_mma, 1);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    if (wid == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(128)
-                     : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const uint32_t tmem_d = tmem_base_slot;
-
-    int ok = 1;
-    for (int kb = 0; kb < nblk && ok; ++kb) {
-        const uint32_t parity = (uint32_t)(kb & 1);
-        if (tid == 0) {
-            // rows past the slice's end but inside M belong to the next slice: the tensor maps cannot mask
-            // them, so slices are whole multiples of kTok and only the last one meets the end of the matrix
-            const int row = (int)(tok0 + (long long)kb * kTok);
-            mbar_expect_tx(&bar_tma, 2 * kTileBytes);
-#pragma unroll
-            for (int cb = 0; cb < 4; ++cb) {
-                tma_load_2d(reinterpret_cast<unsigned char*>(sG) + cb * kColBlk, &mapG, n0 + cb * 32, row, &bar_tma);
-                tma_load_2d(reinterpret_cast<unsigned char*>(sA) + cb * kColBlk, &mapA, k0 + cb * 32, row, &bar_tma);
-            }
-        }
-        const int landed = mbar_wait(&bar_tma, parity) ? 1 : 0;
-#pragma unroll
-        for (int j = 0; j < kTileBytes / 16 / 128; ++j) {
-            float4 x = reinterpret_cast<float4*>(sG)[j * 128 + tid], y = reinterpret_cast<float4*>(sA)[j * 128 + tid];
-            float4 h, l;
-            split_tf32(x.x, h.x, l.x), split_tf32(x.y, h.y, l.y), split_tf32(x.z, h.z, l.z), split_tf32(x.w, h.w, l.w);
-            reinterpret_cast<float4*>(sG)[j * 128 + tid] = h;
-            reinterpret_cast<float4*>(sGlo)[j * 128 + tid] = l;
-            split_tf32(y.x, h.x, l.x), split_tf32(y.y, h.y, l.y), split_tf32(y.z, h.z, l.z), split_tf32(y.w, h.w, l.w);
-            reinterpret_cast<float4*>(sA)[j * 128 + tid] = h;
-            reinterpret_cast<float4*>(sAlo)[j * 128 + tid] = l;
-        }
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        ok = __syncthreads_and(landed);
-        if (ok) {
-            if (tid == 0) {
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint64_t dG = umma_desc_mn_sw128(smem_u32(sG)), dGl = umma_desc_mn_sw128(smem_u32(sGlo));
-                const uint64_t dA = umma_desc_mn_sw128(smem_u32(sA)), dAl = umma_desc_mn_sw128(smem_u32(sAlo));
-#pragma unroll
-                for (int g = 0; g < kTok / 8; ++g) {  // 8 tokens per MMA: the next 1024-byte group
-                    const uint64_t adv = (uint64_t)(g * (1024 >> 4));
-                    umma_tf32_mn(tmem_d, dGl + adv, dA + adv, (kb | g) != 0);
-                    umma_tf32_mn(tmem_d, dG + adv, dAl + adv, 1u);
-                    umma_tf32_mn(tmem_d, dG + adv, dA + adv, 1u);
-                }
-                umma_commit(&bar_mma);
-            }
-            ok = __syncthreads_and(mbar_wait(&bar_mma, parity) ? 1 : 0);
-        }
-    }
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-
-    if (ok) {
-        // accumulator lane = row of dW (column of G), accumulator column = column of dW (column of A)
-        float* patch = reinterpret_cast<float*>(base) + wid * (32 * 36);
-        float* dst_tile = p.part + (long long)split * p.N * p.Kp;
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-            float v[32];
-            if (nblk > 0) {
-                tmem_ld32(tmem_d + ((uint32_t)(wid * 32) << 16) + (uint32_t)(c * 32), v);
-            } else {
-#pragma unroll
-                for (int i = 0; i < 32; ++i) v[i] = 0.f;
-            }
-#pragma unroll
-            for (int q = 0; q < 8; ++q)
-                *reinterpret_cast<float4*>(patch + lane * 36 + q * 4) = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-            __syncwarp();
-            const int cc = (lane & 7) * 4;
-#pragma unroll
-            for (int rr = 0; rr < 8; ++rr) {
-                const int r = rr * 4 + (lane >> 3);
-                const long long grow = (long long)n0 + wid * 32 + r, gcol = (long long)k0 + c * 32 + cc;
-                if (grow < p.N && gcol < p.Kp)  // Kp is a multiple of 4: whole float4 pieces
-                    *reinterpret_cast<float4*>(dst_tile + grow * p.Kp + gcol) = *reinterpret_cast<const float4*>(patch + r * 36 + cc);
-            }
-            __syncwarp();
-        }
-    } else if (tid == 0) {
-        atomicExch(&p.hdr->error, (unsigned int)B200_ERR_TIMEOUT);
-        for (int i = 0; i < 1000; ++i) __nanosleep(1000);
-    }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    if (wid == 1) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(128) : "memory");
-    }
-}
-
-// ------------------------------------------------------------------------------ pipelined weight gradient
-// The same tile of dW = G^T A with the phases of consecutive token blocks overlapped and the G operand
-// in tensor memory.  288 threads: warps 0-3 split G, warps 4-7 split A, lane 0 of warp 8 asks for the
-// copies and issues the MMAs.  Per stage (two of them): the TMA unit brings the raw G block [32 tokens x 128 columns]
-// (unswizzled: thread f reads column f down the tokens, conflict-free) and the A block (token-major,
-// 32-byte-atom swizzle, as above); the splitters write G's hi and lo halves into tensor memory - feature
-// f is lane f, the 32 tokens are 32 columns - from where the MMAs take them as their A operand, and
-// split the A block in place (hi) and beside it (lo); the issuer launches the 12 MMAs (A from tensor
-// memory, B = the activations, MN-major from shared memory), waits for them and asks for the block after
-// next into the same stage while the splitters are busy with the other stage.  G never goes back to
-// shared memory and is never read from there by the tensor core: a third less shared-memory traffic
-// per block than proj_wgrad_kernel, and no full stop between copy, split and MMA.
+// The phases of consecutive token blocks overlap and the G operand lives in tensor memory.  288 threads:
+// warps 0-3 split G, warps 4-7 split A, lane 0 of warp 8 asks for the copies and issues the MMAs.  Per
+// stage (two of them): the TMA unit brings the raw G block [32 tokens x 128 columns] (unswizzled: thread
+// f reads column f down the tokens, conflict-free) and the A block (token-major, 32-byte-atom swizzle);
+// the G splitters write hi and lo halves into tensor memory - feature f is lane f, the 32 tokens are 32
+// columns - from where the MMAs take them as their A operand; the A splitters split the activation
+// block in place (hi) and beside it (lo); the issuer launches the 12 MMAs (A from tensor memory, B = the
+// activations, MN-major from shared memory), waits for them and asks for the block after next into
+// the same stage while the splitters are busy with the other stage.  G never goes back to shared memory
+// and is never read from there by the tensor core (a third less shared-memory traffic per block than
+// splitting both operands there), and copy, split and MMA of neighbouring blocks run at the same time.
 constexpr int kWgStages = 2;
 constexpr int kWgStageBytes = 3 * kTileBytes;  // raw G, A (hi in place), A lo
 constexpr int kWgSmem = kWgStages * kWgStageBytes + 1024;
@@ -1065,12 +933,9 @@ static ProjWs proj_ws(long long N, long long K1, long long K2) {
 }
 
 
-// Token slices of the weight gradient: enough CTAs to fill every SM (two of the pipelined kernel, which
-// tensor memory bounds, three of the plain one), slices a multiple of kTok.
-#ifndef PROJ_WGRAD_WS
-#define PROJ_WGRAD_WS 1
-#endif
-constexpr int kWgradCtasPerSm = PROJ_WGRAD_WS ? 2 : 3;
+// Token slices of the weight gradient: enough CTAs to fill every SM (two per SM: each holds 256 of the
+// 512 tensor-memory columns), slices a multiple of kTok.
+constexpr int kWgradCtasPerSm = 2;
 struct WgradPlan {
     int n_tiles, k_tiles, splits;
     long long tok_per_split, Kp;
@@ -1206,17 +1071,16 @@ int b200_proj_wgrad(int64_t M, int64_t N, int64_t K, const void* G, int64_t ldg,
     char* base = static_cast<char*>(workspace);
     if (cudaMemsetAsync(base, 0, sizeof(WsHeader), st) != cudaSuccess) return B200_ERR_LAUNCH;
     CUtensorMap mG, mA;
-    // token-major operands of 4-byte elements use the 128-byte swizzle whose unit is a 32-byte chunk; the
-    // pipelined kernel takes G as plain rows of 128 columns (its threads read it, not the tensor core)
-    const bool g_ok = PROJ_WGRAD_WS ? make_map(&mG, (const float*)G, M, N, ldg, kTok, CU_TENSOR_MAP_SWIZZLE_NONE, 128)
-                                    : make_map(&mG, (const float*)G, M, N, ldg, kTok, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
-    if (!g_ok || !make_map(&mA, (const float*)A, M, K, lda, kTok, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) return B200_ERR_LAUNCH;
+    // G as plain rows of 128 columns (threads read it, not the tensor core); the token-major activations of
+    // 4-byte elements in the 128-byte swizzle whose unit is a 32-byte chunk
+    if (!make_map(&mG, (const float*)G, M, N, ldg, kTok, CU_TENSOR_MAP_SWIZZLE_NONE, 128) ||
+        !make_map(&mA, (const float*)A, M, K, lda, kTok, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B))
+        return B200_ERR_LAUNCH;
     static bool configured[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !configured[dev]) {
-        if (cudaFuncSetAttribute(proj_wgrad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem) != cudaSuccess ||
-            cudaFuncSetAttribute(proj_wgrad_ws_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kWgSmem) != cudaSuccess)
+        if (cudaFuncSetAttribute(proj_wgrad_ws_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kWgSmem) != cudaSuccess)
             return B200_ERR_LAUNCH;
         configured[dev] = true;
     }
@@ -1227,10 +1091,7 @@ int b200_proj_wgrad(int64_t M, int64_t N, int64_t K, const void* G, int64_t ldg,
     a.hdr = reinterpret_cast<WsHeader*>(base);
     const long long grid = (long long)w.splits * w.n_tiles * w.k_tiles;
     if (grid > 0x7fffffffLL) return B200_ERR_UNSUPPORTED;
-    if (PROJ_WGRAD_WS)
-        proj_wgrad_ws_kernel<<<(unsigned int)grid, kWgThreads, kWgSmem, st>>>(mG, mA, a);
-    else
-        proj_wgrad_kernel<<<(unsigned int)grid, 128, kGemmSmem, st>>>(mG, mA, a);
+    proj_wgrad_ws_kernel<<<(unsigned int)grid, kWgThreads, kWgSmem, st>>>(mG, mA, a);
     if (cudaGetLastError() != cudaSuccess) return B200_ERR_LAUNCH;
     wgrad_reduce_kernel<<<(unsigned int)((N * K + 255) / 256), 256, 0, st>>>(a.part, w.splits, N, K, w.Kp, (float*)dW, lddw);
     return cudaGetLastError() == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
