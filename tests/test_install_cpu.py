@@ -118,12 +118,18 @@ def test_projection_hooks_install_decline_on_cpu_and_restore(tsfast_models):
 
     torch.manual_seed(0)
     model = tsfast_models.DeepLRU(2, 1, d_model=8, d_state=6, n_layers=1)
+    model_s5 = tsfast_models.DeepS5(2, 1, d_model=8, d_state=6, n_layers=1)
     u = torch.randn(2, 20, 2)
-    want = model(u)
+    want, want_s5 = model(u), model_s5(u)
+    originals = (lru.LRU.forward, s5.S5.forward, lru.LRUBlock.forward, s5.S5Block.forward)
     slots = tsfast_b200.install(fuse_projections=True)
     try:
         assert "scan.projections" in slots
         assert lru.complex_in_proj is not scan.complex_in_proj and s5.real_out_proj is not scan.real_out_proj
+        # the layer and block bodies are wrapped too (parameter prologues, fused readout, fused glue) ...
+        assert all(now is not old for now, old in zip((lru.LRU.forward, s5.S5.forward, lru.LRUBlock.forward,
+                                                       s5.S5Block.forward), originals))
+        assert torch.equal(model_s5(u), want_s5)  # ... and decline CPU tensors
         n = tsfast_b200.accelerate_linears(model)
         assert n == 4  # encoder, LayerNorm, GLU, decoder
         assert torch.equal(model(u), want)
@@ -131,4 +137,5 @@ def test_projection_hooks_install_decline_on_cpu_and_restore(tsfast_models):
     finally:
         tsfast_b200.uninstall()
     assert lru.complex_in_proj is scan.complex_in_proj and s5.real_out_proj is scan.real_out_proj
-    assert torch.equal(model(u), want)
+    assert (lru.LRU.forward, s5.S5.forward, lru.LRUBlock.forward, s5.S5Block.forward) == originals
+    assert torch.equal(model(u), want) and torch.equal(model_s5(u), want_s5)
