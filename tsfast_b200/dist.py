@@ -37,21 +37,22 @@ def allreduce_gradients(params, group=None, average: bool = True) -> int:
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     if world == 1:
         return sum(p.numel() for p in params)
-    flat = torch.cat([(p.grad if p.grad is not None else torch.zeros_like(p)).reshape(-1).to(torch.float32)
-                      for p in params])
-    dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=group)
-    if average:
+    # one flat float32 buffer: a single concatenation in, one collective, one multi-tensor copy out (a
+    # per-parameter loop of small kernels costs more than the collective itself on a fast link)
+    grads = [p.grad if p.grad is not None else torch.zeros_like(p) for p in params]
+    flat = torch.cat([g.reshape(-1).to(torch.float32) for g in grads])
+    nccl = dist.get_backend(group) == "nccl"
+    dist.all_reduce(flat, op=dist.ReduceOp.AVG if (average and nccl) else dist.ReduceOp.SUM, group=group)
+    if average and not nccl:
         flat /= world
-    off = 0
-    for p in params:
-        n = p.numel()
-        chunk = flat[off : off + n].view_as(p).to(p.dtype)
+    pieces = [piece.view_as(p) for piece, p in zip(flat.split([p.numel() for p in params]), params)]
+    have = [(p.grad, piece) for p, piece in zip(params, pieces) if p.grad is not None]
+    if have:
+        torch._foreach_copy_([g for g, _ in have], [piece for _, piece in have])
+    for p, piece in zip(params, pieces):
         if p.grad is None:
-            p.grad = chunk.clone()
-        else:
-            p.grad.copy_(chunk)
-        off += n
-    return off
+            p.grad = piece.to(p.dtype).clone()
+    return flat.numel()
 
 
 def reduce_lane_gradient(grad: torch.Tensor, group=None) -> torch.Tensor:
