@@ -167,6 +167,52 @@ def test_projections_on_tensor_cores_match_float64_reference(tsfast_installed, f
         assert proj_b200.calls == before, "the projections were not restored"
 
 
+@pytest.mark.parametrize("kw", [dict(discretization="bilinear"), dict(clip_eigs=True), dict(conj_sym=False),
+                                dict(step_rescale=0.5, discretization="bilinear", clip_eigs=True),
+                                dict(C_init="complex_normal", conj_sym=False, step_rescale=2.0)])
+def test_s5_layer_variants_through_the_fused_path(tsfast_installed, kw):
+    """tsfast's S5 layer in its other configurations (bilinear map, clipped eigenvalues, full state
+    without conjugate symmetry, rescaled step) with install(fuse_projections=True): the discretisation
+    kernel, the packed input projection, the scan and the readout against the float64 reference path,
+    output, carried state and every parameter gradient."""
+    import tsfast_b200
+    from tsfast.models import use_backend
+    from tsfast.models.architectures.s5 import S5
+    from tsfast_b200 import prologue_b200
+
+    torch.manual_seed(1)
+    layer32 = S5(24, 16, **kw)
+    layer64 = copy.deepcopy(layer32).double().cuda()
+    layer32 = layer32.cuda()
+    if kw.get("clip_eigs"):  # push some eigenvalues over the clip so that the clamp and its cut gradient are exercised
+        with torch.no_grad():
+            layer32.Lambda_re[::3] = 0.02
+            layer64.Lambda_re[::3] = 0.02
+    u = torch.randn(3, 150, 24, device="cuda")
+    g = torch.randn(3, 150, 24, device="cuda")
+    tsfast_b200.install(fuse_projections=True)
+    try:
+        before = prologue_b200.calls
+        with use_backend("auto"):
+            y1, s1 = layer32(u[:, :70], return_state=True)
+            y2, s2 = layer32(u[:, 70:], state=s1, return_state=True)
+            got = torch.cat((y1, y2), dim=1)
+            (got * g).sum().backward()
+        assert prologue_b200.calls - before == 4, "two chunks: two discretisations forward, two backward"
+        with use_backend("reference"):
+            r1, t1 = layer64(u[:, :70].double(), return_state=True)
+            r2, t2 = layer64(u[:, 70:].double(), state=t1, return_state=True)
+            want = torch.cat((r1, r2), dim=1)
+            (want * g.double()).sum().backward()
+        assert _rel(got, want) < MODEL_TOL and _rel(torch.view_as_real(s2), torch.view_as_real(t2)) < MODEL_TOL
+        for (name, p), q in zip(layer32.named_parameters(), layer64.parameters()):
+            assert p.grad is not None, name
+            assert _rel(p.grad, q.grad) < MODEL_TOL, (name, kw)
+    finally:
+        tsfast_b200.uninstall()
+        tsfast_b200.install()  # the module fixture keeps the scan backends installed
+
+
 def test_reference_preference_bypasses_b200(tsfast_installed):
     m = tsfast_installed
     from tsfast.models import use_backend
