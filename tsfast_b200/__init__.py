@@ -16,7 +16,7 @@ Everything runs through ``libb200scan.so`` (``python -m tsfast_b200.build``); no
 back to PyTorch or the CPU.
 """
 
-from . import allpole_b200, conv_b200, dynonet_b200, glue_b200, mamba_b200, prologue_b200, proj_b200
+from . import allpole_b200, conv_b200, dynonet_b200, glue_b200, lru_b200, mamba_b200, prologue_b200, proj_b200
 from .scan import diagonal_recurrence, selective_recurrence
 from .install import accelerate_linears, install, restore_linears, uninstall
 from .status import check_status, track_status

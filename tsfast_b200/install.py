@@ -115,7 +115,7 @@ def _wrap_lru_forward():
     ``y = Re(C x) + D u`` is a single pass over ``y`` on the tensor-core GEMM (``proj_b200.readout``)
     instead of a GEMM, a second GEMM and an addition.  Calls the fused path cannot take (CPU, other
     dtypes, the "eager" backend, another backend preference) go to tsfast's own method."""
-    from . import prologue_b200, proj_b200
+    from . import lru_b200, prologue_b200, proj_b200
 
     lru = importlib.import_module("tsfast.models.architectures.lru")
     s5 = importlib.import_module("tsfast.models.architectures.s5")
@@ -132,6 +132,10 @@ def _wrap_lru_forward():
             return original(self, u, state=state, return_state=return_state)
         # eigenvalues and the gamma-scaled, interleaved input weight in one launch (lru.py:79-83, 97-99)
         lam, W = prologue_b200.lru_prologue(self.nu_log, self.theta_log, self.gamma_log, self.B_re, self.B_im)
+        if u.dim() == 3 and (state is None or (state.dim() == 2 and state.dtype == torch.complex64)):
+            # projection, scan and readout as one op: its adjoint forms the input gradient in one two-product GEMM
+            y, x_last = lru_b200.lru_layer(u, lam, W, lru_b200.readout_weight(self.C_re, self.C_im), self.D, state)
+            return (y, x_last) if return_state else y
         x = lru.diagonal_recurrence(lam, proj_b200.packed_in_proj(u, W), state)
         y = proj_b200.readout(x, self.C_re, self.C_im, u, self.D)
         return (y, x[..., -1, :]) if return_state else y
