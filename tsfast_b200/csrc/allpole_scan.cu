@@ -472,7 +472,7 @@ struct GBlockArgs {
 };
 
 #ifndef GBLOCK_BW_W
-#define GBLOCK_BW_W 2  // (batch row, input channel) warps per CTA of the numerator adjoint
+#define GBLOCK_BW_W 1  // (batch row, input channel) warps per CTA of the numerator adjoint
 #endif
 #ifndef GBLOCK_BW_S
 #define GBLOCK_BW_S 3
@@ -770,8 +770,10 @@ __global__ void __launch_bounds__(32 * W, GBLOCK_MINB) gblock_fwd_kernel(const G
 // 1024-step tiles and, inside a tile, the O pairs of its input:
 //   gub[b, j, NB-1 + t] = sum_i sum_k taps[i,j,k] gw[b, j*O+i, t + k]     (input gradient, tail included)
 //   gtaps[b, i, j, k]   = sum_t gw[b, j*O+i, t] ub[b, j, t + NB-1 - k]    (per batch row; summed by the caller)
-// The input tile is fetched once per tile, every gw tile once; per-thread tap sums live in shared
-// memory ([O][NB][32 lanes]) and are added in lane order at the end, so results are reproducible.
+// The input tile is fetched once per tile, every gw tile once; the tap sums are reduced over the warp
+// with a fixed butterfly per (tile, output) and accumulated in shared memory ([O][NB]) in tile order, so
+// results are reproducible.  One warp per CTA and 29 KB of shared memory each: all (b, j) warps of the
+// benchmark shape are resident at once (seven per SM).
 struct GBlockBwdArgs {
     const float* gw;    // [B, I*O, L]
     const float* ub;    // [B*I, pitch]
@@ -803,11 +805,14 @@ __global__ void __launch_bounds__(32 * W, GBLOCK_BW_MINB) gblock_num_bwd_kernel(
     const long long L = p.L;
     const long long orow = p.split ? b * P + j * p.O + i0 : b * p.I + j;  // row of gub this warp writes
 
-    const int fper = (S + 3) * kStageF + 32 * kChunk + O * NB * 32;
+    // input tiles in flight: the S-1 items requested ahead span at most two tiles when a warp walks several
+    // outputs per tile, three when it walks one (split mode)
+    const int UB = p.split ? 3 : 2;
+    const int fper = (S + UB) * kStageF + 32 * kChunk + O * NB;
     float* ring = reinterpret_cast<float*>(smem_raw) + (size_t)w * fper;  // [S] gw tiles
-    float* ubuf = ring + S * kStageF;                                       // [3] input tiles
-    float* gstage = ubuf + 3 * kStageF;                                     // [32][kChunk] output staging
-    float* gbs = gstage + 32 * kChunk;                                      // [O][NB][32]
+    float* ubuf = ring + S * kStageF;                                       // [UB] input tiles
+    float* gstage = ubuf + UB * kStageF;                                    // [32][kChunk] output staging
+    float* gbs = gstage + 32 * kChunk;                                      // [O][NB] tap sums (lane 0 adds the warp's sum per item)
     // tap sums start at zero; the tiles too, so that what a short last tile leaves uncopied is finite
     for (int e = lid; e < fper; e += 32) ring[e] = 0.f;
     __syncwarp();
@@ -834,7 +839,7 @@ __global__ void __launch_bounds__(32 * W, GBLOCK_BW_MINB) gblock_num_bwd_kernel(
         const long long c = q / ni, i = i0 + (q - c * ni);
         // gw rows are L long (L % 4 == 0 when VEC == 4): whole pieces only below L
         copy_tile(ring + slot * kStageF, p.gw + (b * P + j * p.O + i) * L + c * kTile, L - c * kTile);
-        if (i == i0) copy_tile(ubuf + (int)(c % 3) * kStageF, p.ub + (b * p.I + j) * p.pitch + c * kTile, p.pitch - c * kTile);
+        if (i == i0) copy_tile(ubuf + (int)(c % UB) * kStageF, p.ub + (b * p.I + j) * p.pitch + c * kTile, p.pitch - c * kTile);
     };
 #pragma unroll
     for (int q = 0; q < S - 1; ++q) {
@@ -868,7 +873,7 @@ __global__ void __launch_bounds__(32 * W, GBLOCK_BW_MINB) gblock_num_bwd_kernel(
             cp_wait<S - 2>();
             __syncwarp();
             if (i == i0) {  // this tile's input samples: own chunk and the first NB-1 of the next one
-                const float* ut = ubuf + (int)(c % 3) * kStageF;
+                const float* ut = ubuf + (int)(c % UB) * kStageF;
 #pragma unroll
                 for (int r = 0; r < kSeg / 4; ++r) {
                     const float4 t4 = *reinterpret_cast<const float4*>(ut + lid * kChunk + 4 * r);
@@ -921,13 +926,16 @@ __global__ void __launch_bounds__(32 * W, GBLOCK_BW_MINB) gblock_num_bwd_kernel(
                 for (int k = 0; k < NB; ++k) acc = fmaf(bt[k], gc[r + k], acc);
                 guacc[r] = acc;
             }
-            float* gb = gbs + ((i - i0) * NB) * 32 + lid;
+            float* gb = gbs + (i - i0) * NB;
 #pragma unroll
             for (int k = 0; k < NB; ++k) {
                 float acc = 0.f;
 #pragma unroll
                 for (int r = 0; r < kSeg; ++r) acc = fmaf(gc[r], uc[r + NB - 1 - k], acc);
-                gb[k * 32] += acc;
+                // the warp's sum in a fixed (butterfly) order, added to the running tap sum by lane 0
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+                if (lid == 0) gb[k] += acc;
             }
         }
         // the input gradient of this tile: staged, then stored as coalesced 4-byte rows (its
@@ -946,18 +954,16 @@ __global__ void __launch_bounds__(32 * W, GBLOCK_BW_MINB) gblock_num_bwd_kernel(
     }
     cp_wait<0>();
     __syncwarp();
-    for (int e = lid; e < ni * NB; e += 32) {  // e = (i-i0)*NB + k: add the 32 lane sums in lane order
-        float acc = 0.f;
-        for (int l = 0; l < 32; ++l) acc += gbs[e * 32 + l];
+    for (int e = lid; e < ni * NB; e += 32) {  // e = (i-i0)*NB + k
         const int i = i0 + e / NB, k = e % NB;
-        p.gtaps[((b * p.O + i) * p.I + j) * NB + k] = acc;
+        p.gtaps[((b * p.O + i) * p.I + j) * NB + k] = gbs[e];
     }
 }
 
 template <int NB, int VEC>
 static int launch_gblock_num_bwd(const GBlockBwdArgs& a, cudaStream_t st) {
     constexpr int W = GBLOCK_BW_W, S = GBLOCK_BW_S;
-    const size_t fper = (size_t)(S + 3) * 33 * 36 + 32 * 36 + (size_t)a.O * NB * 32;
+    const size_t fper = (size_t)(S + (a.split ? 3 : 2)) * 33 * 36 + 32 * 36 + (size_t)a.O * NB;
     const size_t smem = W * fper * sizeof(float);
     if (smem > 200 * 1024) return B200_ERR_UNSUPPORTED;
     auto kern = gblock_num_bwd_kernel<NB, VEC, W, S>;
