@@ -1016,7 +1016,7 @@ __global__ void gblock_pack_rows_kernel(const float* __restrict__ u, const float
 #define GBLOCK_SEG 32  // steps per thread of the forward (16 or 32)
 #endif
 #ifndef GBLOCK_W
-#define GBLOCK_W 2  // (batch row, output channel) warps per CTA
+#define GBLOCK_W 1  // (batch row, output channel) warps per CTA (1 measured 2.5 % faster than 2 at B=128, T=8192, 128 filters)
 #endif
 #ifndef GBLOCK_S
 #define GBLOCK_S 2  // ring stages per warp (2 measured 5 % faster than 3 at B=128, T=8192, 128 filters)
